@@ -32,10 +32,25 @@ class Cache:
             vd = g.head_dim if g.v_head_dim is None else g.v_head_dim
             self.keys.append(torch.empty((n, n_pages, g.kv_heads, PAGE_TOKENS, g.head_dim), dtype=dtype, device=device))
             self.values.append(torch.empty((n, n_pages, g.kv_heads, PAGE_TOKENS, vd), dtype=dtype, device=device) if vd else None)
-        self.states: dict[int, torch.Tensor] = {}
+        self._state_tensors: list[torch.Tensor] = []
+
+        def make(req):
+            # one tensor a request, a dictionary of tensors for a mapping of requests
+            if req is None:
+                return None
+            if isinstance(req, dict):
+                return {name: make(r) for name, r in req.items()}
+            t = torch.zeros((max_seqs + 1, *req.shape), dtype=req.dtype, device=device)
+            self._state_tensors.append(t)
+            return t
+
+        self.states: dict[int, object] = {}
+        self.block_states: dict[int, object] = {}
         for i, e in enumerate(plan.entries):
             if e.state is not None:
-                self.states[i] = torch.zeros((max_seqs + 1, *e.state.shape), dtype=e.state.dtype, device=device)
+                self.states[i] = make(e.state)
+            if getattr(e, "block_state", None) is not None:
+                self.block_states[i] = make(e.block_state)
         self.views: list[CacheView] = []
         for i, e in enumerate(plan.entries):
             src = plan.entries[e.source] if e.source is not None else e
@@ -44,14 +59,15 @@ class Cache:
                 k = self.keys[src.group][src.index_in_group]
                 v = self.values[src.group][src.index_in_group] if self.values[src.group] is not None else None
             self.views.append(CacheView(group=src.group if src.group is not None else 0, k=k, v=v,
-                                        writes=e.source is None, state=self.states.get(i)))
+                                        writes=e.source is None, state=self.states.get(i),
+                                        block_state=self.block_states.get(i)))
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in [*self.keys, *self.values, *self.states.values()] if t is not None)
+        return sum(t.numel() * t.element_size() for t in [*self.keys, *self.values, *self._state_tensors] if t is not None)
 
     def open(self) -> int:
         slot = self.pages.open()
-        for t in self.states.values():
+        for t in self._state_tensors:
             t[slot].zero_()
         return slot
 

@@ -36,7 +36,7 @@ class LayerSpec:
     """One layer: how its parts are arranged (`block`), and the parts."""
     block: PartSpec                 # arrangement, e.g. pre-norm residual block
     mixer: PartSpec                 # token mixer, e.g. grouped-query attention
-    ffn: PartSpec                   # feed-forward, dense or routed
+    ffn: Optional[PartSpec]         # feed-forward, dense or routed; None: the layer has none
     norms: Mapping[str, PartSpec]   # named norms the block places (e.g. "mixer", "ffn")
     prefix: str                     # tensor-name prefix of this layer's weights
 

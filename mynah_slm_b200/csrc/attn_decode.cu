@@ -29,8 +29,10 @@ struct DecodeArgs {
     int H, KV, HD, ldq, ldo;
     int window;          // 0: all keys
     int S;               // pages a sequence may see at most (grid size and scratch stride)
-    int lpk;             // lanes per key: power of two >= HD/8, <= 32
+    int lpk;             // lanes per key: power of two >= max(HD, VD)/8, <= 32
     float scale;
+    int VD;              // width of a value head
+    int chunk;           // 0: none; C: the query at position p sees keys from floor(p / C) * C on
 };
 
 template <int GT>
@@ -51,13 +53,14 @@ attn_decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int lpk = a.lpk, kpw = 32 / lpk;
     const int u = lane % lpk, slot = lane / lpk;
-    const int HD = a.HD;
-    const bool lane_on = u * 8 < HD;
+    const int HD = a.HD, VD = a.VD;
+    const bool lane_on = u * 8 < HD, lane_on_v = u * 8 < VD;
 
     // key range of this split: the s-th page of the visible range
     const int hi = kv_len[b];
     int lo = 0;
     if (a.window > 0) lo = max(0, hi - a.window);
+    if (a.chunk > 0 && hi > 0) lo = max(lo, ((hi - 1) / a.chunk) * a.chunk);
     int key_begin = 0, key_end = 0;
     if (hi > 0) {
         const int pg0 = lo / PAGE_TOKENS, pg1 = (hi - 1) / PAGE_TOKENS + 1;
@@ -101,10 +104,10 @@ attn_decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
             if (page >= pt.n_pages) page = -1;
             if (page < 0) {
                 bad_page = true;
-            } else if (lane_on) {
-                const size_t off = (((size_t)page * a.KV + g) * PAGE_TOKENS + key % PAGE_TOKENS) * HD + u * 8;
-                load8(k_cache + off, kf);
-                load8(v_cache + off, vf);
+            } else {
+                const size_t tok = ((size_t)page * a.KV + g) * PAGE_TOKENS + key % PAGE_TOKENS;
+                if (lane_on) load8(k_cache + tok * HD + u * 8, kf);
+                if (lane_on_v) load8(v_cache + tok * VD + u * 8, vf);
             }
             have = page >= 0;
         }
@@ -148,20 +151,22 @@ attn_decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
     }
     __shared__ float sm_m[WARPS][GT], sm_l[WARPS][GT];
     __shared__ float sm_o[WARPS][GT][256];
-    if (slot == 0 && lane_on) {
+    if (slot == 0 && (lane_on_v || u == 0)) {
 #pragma unroll
         for (int i = 0; i < GT; i++) {
             if (u == 0) {
                 sm_m[warp][i] = st.m[i];
                 sm_l[warp][i] = st.l[i];
             }
+            if (lane_on_v) {
 #pragma unroll
-            for (int j = 0; j < 8; j++) sm_o[warp][i][u * 8 + j] = st.acc[i][j];
+                for (int j = 0; j < 8; j++) sm_o[warp][i][u * 8 + j] = st.acc[i][j];
+            }
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < n_heads * HD; idx += blockDim.x) {
-        const int i = idx / HD, d = idx % HD;
+    for (int idx = threadIdx.x; idx < n_heads * VD; idx += blockDim.x) {
+        const int i = idx / VD, d = idx % VD;
         float mn = -INFINITY;
 #pragma unroll
         for (int w = 0; w < WARPS; w++) mn = fmaxf(mn, sm_m[w][i]);
@@ -173,7 +178,7 @@ attn_decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
             os += sm_o[w][i][d] * aw;
         }
         const size_t row = ((size_t)b * a.H + (h0 + i)) * a.S + s;
-        part_o[row * HD + d] = os;
+        part_o[row * VD + d] = os;
         if (d == 0) {
             part_ml[row * 2] = mn;
             part_ml[row * 2 + 1] = ls;
@@ -183,13 +188,14 @@ attn_decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
 
 template <typename T>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                           T* __restrict__ out, const int* __restrict__ kv_len, int window,
+                                           T* __restrict__ out, const int* __restrict__ kv_len, int window, int chunk,
                                            int H, int HD, int S_max, int ldo) {
     const int h = blockIdx.x, b = blockIdx.y;
     const size_t row0 = ((size_t)b * H + h) * S_max;
     // only the pages the sequence can see have partial results
     const int hi = kv_len[b];
-    const int lo = window > 0 ? max(0, hi - window) : 0;
+    int lo = window > 0 ? max(0, hi - window) : 0;
+    if (chunk > 0 && hi > 0) lo = max(lo, ((hi - 1) / chunk) * chunk);
     const int S = hi > 0 ? min(S_max, (hi - 1) / PAGE_TOKENS + 1 - lo / PAGE_TOKENS) : 0;
     float mn = -INFINITY;
     for (int s = 0; s < S; s++) mn = fmaxf(mn, part_ml[(row0 + s) * 2]);
@@ -227,8 +233,8 @@ int launch_decode(const void* q, void* out, int B, const DecodeArgs& a, const vo
     else
         attn_decode_split_kernel<T, 4><<<grid, WARPS * 32, 0, stream>>>(qp, kp, vp, kv_len, pt, a, part_o, part_ml, status);
     if (mynah_check_launch("attn_decode_split")) return -1;
-    const int threads = a.HD >= 128 ? 128 : (a.HD >= 64 ? 64 : 32);
-    attn_decode_combine_kernel<T><<<dim3(a.H, B), threads, 0, stream>>>(part_o, part_ml, (T*)out, kv_len, a.window, a.H, a.HD, a.S, a.ldo);
+    const int threads = a.VD >= 128 ? 128 : (a.VD >= 64 ? 64 : 32);
+    attn_decode_combine_kernel<T><<<dim3(a.H, B), threads, 0, stream>>>(part_o, part_ml, (T*)out, kv_len, a.window, a.chunk, a.H, a.VD, a.S, a.ldo);
     return mynah_check_launch("attn_decode_combine");
 }
 
@@ -240,6 +246,15 @@ MYNAH_API long long mynah_attn_decode_scratch_floats(int B, int H, int HD, int n
     return (long long)B * H * n_splits * (HD + 2);
 }
 
+// The general form: value heads of their own width VD (a multiple of 8 up to 256; out has head h at columns
+// [h*VD, (h+1)*VD); scratch of B * H * n_splits * (VD + 2) floats), a score scale given by the caller
+// (0: 1/sqrt(HD)) and a chunk mask (0: none) beside the window.
+MYNAH_API int mynah_attn_decode_ex(
+    const void* q, void* out, int dtype, int B, int H, int KV, int HD, int VD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int chunk, float scale, int n_splits, float* scratch, int* status, cudaStream_t stream);
+
 // q: [B, ldq], one row per sequence; out: [B, ldo]. head_dim must be a
 // multiple of 8 (16-byte rows) and at most 256.
 MYNAH_API int mynah_attn_decode(
@@ -247,19 +262,30 @@ MYNAH_API int mynah_attn_decode(
     const void* k_cache, const void* v_cache, const int* kv_len,
     const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
     int window, int n_splits, float* scratch, int* status, cudaStream_t stream) {
+    return mynah_attn_decode_ex(q, out, dtype, B, H, KV, HD, HD, ldq, ldo, k_cache, v_cache, kv_len, page_indptr, page_ids,
+                                page_base, n_pages, window, 0, 0.f, n_splits, scratch, status, stream);
+}
+
+MYNAH_API int mynah_attn_decode_ex(
+    const void* q, void* out, int dtype, int B, int H, int KV, int HD, int VD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int chunk, float scale, int n_splits, float* scratch, int* status, cudaStream_t stream) {
     if (B == 0) return 0;
     MYNAH_REQUIRE(B > 0 && H > 0 && KV > 0 && HD > 0 && H % KV == 0, "attn_decode: bad sizes B=%d H=%d KV=%d HD=%d", B, H, KV, HD);
     MYNAH_REQUIRE(HD % 8 == 0 && HD <= 256, "attn_decode: head_dim %d must be a multiple of 8 and at most 256", HD);
+    MYNAH_REQUIRE(VD > 0 && VD % 8 == 0 && VD <= 256, "attn_decode: a value head of %d must be a multiple of 8 and at most 256", VD);
+    MYNAH_REQUIRE(chunk >= 0, "attn_decode: negative chunk");
     MYNAH_REQUIRE(ldq % 8 == 0, "attn_decode: query row stride %d must be a multiple of 8", ldq);
     MYNAH_REQUIRE(n_splits >= 1 && n_splits <= 65535, "attn_decode: bad split count %d", n_splits);
     MYNAH_REQUIRE(B <= 65535, "attn_decode: batch %d exceeds one launch", B);
     MYNAH_REQUIRE(scratch != nullptr, "attn_decode: no scratch memory given");
     int lpk = 1;
-    while (lpk * 8 < HD) lpk <<= 1;
-    const DecodeArgs a{H, KV, HD, ldq, ldo, window, n_splits, lpk, 1.0f / sqrtf((float)HD)};
+    while (lpk * 8 < HD || lpk * 8 < VD) lpk <<= 1;
+    const DecodeArgs a{H, KV, HD, ldq, ldo, window, n_splits, lpk, scale != 0.f ? scale : 1.0f / sqrtf((float)HD), VD, chunk};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
     float* part_o = scratch;
-    float* part_ml = scratch + (size_t)B * H * n_splits * HD;
+    float* part_ml = scratch + (size_t)B * H * n_splits * VD;
     if (dtype == MYNAH_F32)
         return launch_decode<float>(q, out, B, a, k_cache, v_cache, kv_len, pt, part_o, part_ml, status, stream);
     if (dtype == MYNAH_BF16)

@@ -28,6 +28,8 @@ struct PrefillArgs {
     int B, H, KV, HD, ldq, ldo;
     int window;                 // 0: all keys
     float scale;
+    int VD;                     // width of a value head (HD unless the mixer's values are narrower or wider)
+    int chunk;                  // 0: none; C: a query at position p sees keys from floor(p / C) * C on
 };
 
 template <typename TA, typename TC>
@@ -37,10 +39,10 @@ attn_prefill_generic_kernel(const TA* __restrict__ q, TA* __restrict__ out,
                             const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                             PageTable pt, PrefillArgs a, int* __restrict__ status) {
     extern __shared__ float smem[];
-    const int HD = a.HD, KS = HD + 1;                 // padded key rows: lanes read distinct banks
+    const int HD = a.HD, VD = a.VD, KS = HD + 1;      // padded key rows: lanes read distinct banks
     float* Ks = smem;                                  // [KT][HD+1]
-    float* Vs = Ks + KT * KS;                          // [KT][HD]
-    float* Qs = Vs + KT * HD;                          // [QT][HD]
+    float* Vs = Ks + KT * KS;                          // [KT][VD]
+    float* Qs = Vs + KT * VD;                          // [QT][HD]
 
     int b, tile;
     if (!find_query_tile(cu_q, a.B, QT, blockIdx.x, b, tile)) return;   // blockIdx.x numbers the step's query tiles
@@ -70,6 +72,7 @@ attn_prefill_generic_kernel(const TA* __restrict__ q, TA* __restrict__ out,
     const int p_first = past + tile0, p_last = past + tile0 + nq - 1;
     int k_lo = 0;
     if (a.window > 0) k_lo = max(0, p_first - a.window + 1);
+    if (a.chunk > 0) k_lo = max(k_lo, (p_first / a.chunk) * a.chunk);
     k_lo = (k_lo / KT) * KT;
 
     for (int kt = k_lo; kt <= p_last; kt += KT) {
@@ -80,13 +83,14 @@ attn_prefill_generic_kernel(const TA* __restrict__ q, TA* __restrict__ out,
             return;                                    // uniform over the CTA
         }
         const size_t base = (((size_t)page * a.KV + kvh) * PAGE_TOKENS + kt % PAGE_TOKENS) * HD;
+        const size_t vbase = (((size_t)page * a.KV + kvh) * PAGE_TOKENS + kt % PAGE_TOKENS) * VD;
         const int n_keys = min(KT, n_kv - kt);         // rows past the sequence's end are not read
         for (int i = threadIdx.x; i < KT * HD; i += blockDim.x) {
             const int j = i / HD, d = i % HD;
-            const bool ok = j < n_keys;
-            Ks[j * KS + d] = ok ? to_f32(k_cache[base + i]) : 0.f;
-            Vs[i] = ok ? to_f32(v_cache[base + i]) : 0.f;
+            Ks[j * KS + d] = j < n_keys ? to_f32(k_cache[base + i]) : 0.f;
         }
+        for (int i = threadIdx.x; i < KT * VD; i += blockDim.x)
+            Vs[i] = i / VD < n_keys ? to_f32(v_cache[vbase + i]) : 0.f;
         __syncthreads();
 
 #pragma unroll
@@ -101,6 +105,7 @@ attn_prefill_generic_kernel(const TA* __restrict__ q, TA* __restrict__ out,
             for (int d = 0; d < HD; d++) dot = fmaf(qrow[d], krow[d], dot);
             bool vis = key <= p && key < n_kv;
             if (a.window > 0) vis = vis && key > p - a.window;
+            if (a.chunk > 0) vis = vis && key >= (p / a.chunk) * a.chunk;
             const float s = vis ? dot * a.scale : -INFINITY;
             const float m_new = fmaxf(m[i], warp_max(s));
             if (m_new == -INFINITY) continue;          // no visible key yet (uniform)
@@ -115,7 +120,7 @@ attn_prefill_generic_kernel(const TA* __restrict__ q, TA* __restrict__ out,
 #pragma unroll
                 for (int c = 0; c < MAXC; c++) {
                     const int d = lane + 32 * c;
-                    if (d < HD) acc[i][c] = fmaf(pb, Vs[j * HD + d], acc[i][c]);
+                    if (d < VD) acc[i][c] = fmaf(pb, Vs[j * VD + d], acc[i][c]);
                 }
             }
         }
@@ -126,16 +131,24 @@ attn_prefill_generic_kernel(const TA* __restrict__ q, TA* __restrict__ out,
         const int qi = warp * QPW + i;
         if (qi >= nq) continue;
         const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
-        TA* o = out + (size_t)(q0 + tile0 + qi) * a.ldo + (size_t)h * HD;
+        TA* o = out + (size_t)(q0 + tile0 + qi) * a.ldo + (size_t)h * VD;
 #pragma unroll
         for (int c = 0; c < MAXC; c++) {
             const int d = lane + 32 * c;
-            if (d < HD) o[d] = from_f32<TA>(acc[i][c] * inv);
+            if (d < VD) o[d] = from_f32<TA>(acc[i][c] * inv);
         }
     }
 }
 
 }  // namespace
+
+// The general form: value heads of their own width VD (out has head h at columns [h*VD, (h+1)*VD)), a score
+// scale given by the caller (0: 1/sqrt(HD)), and a chunk mask (0: none) beside the window.
+MYNAH_API int mynah_attn_prefill_generic_ex(
+    const void* q, void* out, int dtype, int n_tokens, int B, int max_q_len, int H, int KV, int HD, int VD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* cu_q, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int chunk, float scale, int* status, cudaStream_t stream);
 
 // q: [T, ldq] with head h at columns [h*HD, (h+1)*HD); out: [T, ldo] likewise.
 MYNAH_API int mynah_attn_prefill_generic(
@@ -143,14 +156,26 @@ MYNAH_API int mynah_attn_prefill_generic(
     const void* k_cache, const void* v_cache, const int* cu_q, const int* kv_len,
     const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
     int window, int* status, cudaStream_t stream) {
+    return mynah_attn_prefill_generic_ex(q, out, dtype, n_tokens, B, max_q_len, H, KV, HD, HD, ldq, ldo, k_cache, v_cache,
+                                         cu_q, kv_len, page_indptr, page_ids, page_base, n_pages, window, 0, 0.f, status,
+                                         stream);
+}
+
+MYNAH_API int mynah_attn_prefill_generic_ex(
+    const void* q, void* out, int dtype, int n_tokens, int B, int max_q_len, int H, int KV, int HD, int VD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* cu_q, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int chunk, float scale, int* status, cudaStream_t stream) {
     if (B == 0 || max_q_len == 0) return 0;
     MYNAH_REQUIRE(B > 0 && H > 0 && KV > 0 && HD > 0 && H % KV == 0, "attn_prefill: bad sizes B=%d H=%d KV=%d HD=%d", B, H, KV, HD);
     MYNAH_REQUIRE(HD <= 32 * MAXC, "attn_prefill: head_dim %d exceeds %d", HD, 32 * MAXC);
+    MYNAH_REQUIRE(VD > 0 && VD <= 32 * MAXC, "attn_prefill: value head of %d lies outside 1..%d", VD, 32 * MAXC);
+    MYNAH_REQUIRE(chunk >= 0, "attn_prefill: negative chunk");
     MYNAH_REQUIRE(H <= 65535, "attn_prefill: H=%d exceeds one launch", H);
     MYNAH_REQUIRE(window >= 0, "attn_prefill: negative window");
-    const PrefillArgs a{B, H, KV, HD, ldq, ldo, window, 1.0f / sqrtf((float)HD)};
+    const PrefillArgs a{B, H, KV, HD, ldq, ldo, window, scale != 0.f ? scale : 1.0f / sqrtf((float)HD), VD, chunk};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
-    const size_t smem = sizeof(float) * ((size_t)KT * (HD + 1) + (size_t)KT * HD + (size_t)QT * HD);
+    const size_t smem = sizeof(float) * ((size_t)KT * (HD + 1) + (size_t)KT * VD + (size_t)QT * HD);
     (void)max_q_len;
     MYNAH_REQUIRE(n_tokens >= 0, "attn_prefill: negative row count");
     const dim3 grid(ceil_div(n_tokens, QT) + B, H, 1);               // the most query tiles that n_tokens rows in B sequences make

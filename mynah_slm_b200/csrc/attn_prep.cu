@@ -1,0 +1,158 @@
+// What lies between the q/k/v projection and the attention for mixers that norm the WHOLE projection:
+//
+//   q <- q / rms(q over all heads) * wq          (one RMS over the H*dim outputs, gain of that size; k likewise)
+//   rotary positions on the first `rot` dimensions of each head of q and k, element i paired with i + rot/2:
+//       (u, v) -> (u cos a - v sin a, v cos a + u sin a),   a = position * base^(-2i/rot)   (tables built in double)
+//   v <- v / rms(v over the head's vd values)     (no gain)
+//   v <- (1 - lambda) v + lambda v_first          (optional: v_first holds the same token's values of an earlier
+//                                                  layer, written here by the layer that comes first)
+//   q -> q_out, k and v -> the paged cache
+//
+// Everything is computed in fp32 from the projection's rows. Heads may be narrower than their storage: q_out and
+// the cache hold dimp >= dim and vdp >= vd elements a head (multiples of 8), the rest written as zeros, which
+// changes neither a score nor a used output column.
+#include "layout.cuh"
+
+namespace {
+
+struct PrepArgs {
+    int H, G, dim, vd, dimp, vdp, ld, ldq, rot, n_pos;
+    float eps;
+    int vmix;        // 0: none, 1: write v_first, 2: mix with v_first
+};
+
+constexpr int PREP_THREADS = 128;
+
+template <typename T>
+__device__ __forceinline__ float normed_rotated(const T* __restrict__ src, const VecRef& gain, int head0, int d, float r,
+                                                const float* __restrict__ cosr, const float* __restrict__ sinr, int rot) {
+    // src: the projection's row; head0: index of the head's first element in the projection (and in the gain)
+    const float x = to_f32(src[head0 + d]) * r * gain.at(head0 + d);
+    if (d >= rot) return x;
+    const int half = rot >> 1;
+    if (d < half) {
+        const float y = to_f32(src[head0 + d + half]) * r * gain.at(head0 + d + half);
+        return x * cosr[d] - y * sinr[d];
+    }
+    const int j = d - half;
+    const float y = to_f32(src[head0 + j]) * r * gain.at(head0 + j);
+    return x * cosr[j] + y * sinr[j];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(PREP_THREADS)
+attn_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, VecRef qw, VecRef kw,
+                 const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                 const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, PageTable pt,
+                 T* __restrict__ k_cache, T* __restrict__ v_cache, float* __restrict__ v_first,
+                 const float* __restrict__ lambda_p, PrepArgs a, int* __restrict__ status) {
+    __shared__ float red[32];
+    griddep_launch_small();
+    griddep_wait();
+    const int row = blockIdx.x;
+    const int b = tok_seq[row];
+    T* qo = q_out + (size_t)row * a.ldq;
+    const int nq = a.H * a.dim, nk = a.G * a.dim;
+    if (b < 0) {                                   // a padding row: defined zeros, nothing cached
+        for (int i = threadIdx.x; i < a.H * a.dimp; i += PREP_THREADS) qo[i] = from_f32<T>(0.f);
+        return;
+    }
+    const T* src = qkv + (size_t)row * a.ld;
+    const int pos = tok_pos[row];
+    if (a.rot > 0 && (pos < 0 || pos >= a.n_pos)) {
+        if (threadIdx.x == 0) atomicOr(status, MYNAH_ST_POS_RANGE);
+        return;
+    }
+    const float* cosr = a.rot > 0 ? cos_t + (size_t)pos * (a.rot >> 1) : nullptr;
+    const float* sinr = a.rot > 0 ? sin_t + (size_t)pos * (a.rot >> 1) : nullptr;
+
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < nq; i += PREP_THREADS) {
+        const float v = to_f32(src[i]);
+        sq = fmaf(v, v, sq);
+    }
+    const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)nq + a.eps);
+    for (int i = threadIdx.x; i < a.H * a.dimp; i += PREP_THREADS) {
+        const int h = i / a.dimp, d = i % a.dimp;
+        qo[i] = from_f32<T>(d < a.dim ? normed_rotated(src, qw, h * a.dim, d, rq, cosr, sinr, a.rot) : 0.f);
+    }
+    if (k_cache == nullptr) return;                // this run reads a cache that another run wrote
+
+    const int page = page_of(pt, b, pos);
+    if (page < 0) {
+        if (threadIdx.x == 0) atomicOr(status, MYNAH_ST_PAGE_RANGE);
+        return;
+    }
+    const T* ksrc = src + nq;
+    float sk = 0.f;
+    for (int i = threadIdx.x; i < nk; i += PREP_THREADS) {
+        const float v = to_f32(ksrc[i]);
+        sk = fmaf(v, v, sk);
+    }
+    const float rk = 1.0f / sqrtf(block_sum(sk, red) / (float)nk + a.eps);
+    const int in_page = pos % PAGE_TOKENS;
+    for (int i = threadIdx.x; i < a.G * a.dimp; i += PREP_THREADS) {
+        const int g = i / a.dimp, d = i % a.dimp;
+        const float v = d < a.dim ? normed_rotated(ksrc, kw, g * a.dim, d, rk, cosr, sinr, a.rot) : 0.f;
+        k_cache[(((size_t)page * a.G + g) * PAGE_TOKENS + in_page) * a.dimp + d] = from_f32<T>(v);
+    }
+
+    // values: a warp a head
+    const T* vsrc = ksrc + nk;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float lam = a.vmix == 2 ? *lambda_p : 0.f;
+    for (int g = warp; g < a.G; g += PREP_THREADS / 32) {
+        float sv = 0.f;
+        for (int d = lane; d < a.vd; d += 32) {
+            const float v = to_f32(vsrc[g * a.vd + d]);
+            sv = fmaf(v, v, sv);
+        }
+        const float rv = 1.0f / sqrtf(warp_sum(sv) / (float)a.vd + a.eps);
+        T* dst = v_cache + (((size_t)page * a.G + g) * PAGE_TOKENS + in_page) * a.vdp;
+        float* vf = v_first ? v_first + ((size_t)row * a.G + g) * a.vd : nullptr;
+        for (int d = lane; d < a.vdp; d += 32) {
+            float v = 0.f;
+            if (d < a.vd) {
+                v = to_f32(vsrc[g * a.vd + d]) * rv;
+                if (a.vmix == 1) vf[d] = v;
+                else if (a.vmix == 2) v = (1.0f - lam) * v + lam * vf[d];
+            }
+            dst[d] = from_f32<T>(v);
+        }
+    }
+}
+
+}  // namespace
+
+// qkv [T, ld]: H*dim query, then G*dim key, then G*vd value outputs a row. q_out [T, ldq] with head h at
+// h*dimp. Caches [n_pages][G][PAGE_TOKENS][dimp | vdp]; null caches: only q is made. cos/sin [n_pos, rot/2]
+// fp32 (rot 0: no rotation). v_first fp32 [T, G*vd]; lambda: one fp32 on the device.
+MYNAH_API int mynah_attn_prep(const void* qkv, int dtype, int T, int ld, void* q_out, int ldq,
+                              int H, int G, int dim, int vd, int dimp, int vdp,
+                              const void* q_gain, const void* k_gain, int gain_dtype, float eps,
+                              const float* cos_t, const float* sin_t, int rot, int n_pos,
+                              const int* tok_seq, const int* tok_pos,
+                              const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+                              void* k_cache, void* v_cache, float* v_first, const float* lambda_p, int vmix,
+                              int* status, cudaStream_t stream) {
+    if (T == 0) return 0;
+    MYNAH_REQUIRE(T > 0 && H > 0 && G > 0 && dim > 0 && vd > 0, "attn_prep: bad sizes T=%d H=%d G=%d dim=%d vd=%d", T, H, G, dim, vd);
+    MYNAH_REQUIRE(dimp >= dim && vdp >= vd, "attn_prep: stored heads are narrower than the heads");
+    MYNAH_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= dim, "attn_prep: %d rotated dimensions do not fit a head of %d", rot, dim);
+    MYNAH_REQUIRE(rot == 0 || (cos_t && sin_t), "attn_prep: no rotation tables given");
+    MYNAH_REQUIRE(q_gain && k_gain, "attn_prep: no gains given");
+    MYNAH_REQUIRE((k_cache == nullptr) == (v_cache == nullptr), "attn_prep: keys and values are cached together");
+    MYNAH_REQUIRE(vmix == 0 || (v_first != nullptr && (vmix == 1 || lambda_p != nullptr)), "attn_prep: value mixing needs its buffers");
+    const PrepArgs a{H, G, dim, vd, dimp, vdp, ld, ldq, rot, n_pos, eps, vmix};
+    const PageTable pt{page_indptr, page_ids, page_base, n_pages};
+    const VecRef qw{q_gain, gain_dtype}, kw{k_gain, gain_dtype};
+    if (dtype == MYNAH_F32)
+        mynah_launch(attn_prep_kernel<float>, dim3(T), dim3(PREP_THREADS), 0, stream, (const float*)qkv, (float*)q_out, qw, kw,
+                     cos_t, sin_t, tok_seq, tok_pos, pt, (float*)k_cache, (float*)v_cache, v_first, lambda_p, a, status);
+    else if (dtype == MYNAH_BF16)
+        mynah_launch(attn_prep_kernel<bf16>, dim3(T), dim3(PREP_THREADS), 0, stream, (const bf16*)qkv, (bf16*)q_out, qw, kw,
+                     cos_t, sin_t, tok_seq, tok_pos, pt, (bf16*)k_cache, (bf16*)v_cache, v_first, lambda_p, a, status);
+    else
+        return mynah_fail("attn_prep: unsupported dtype %d", dtype);
+    return mynah_check_launch("attn_prep");
+}

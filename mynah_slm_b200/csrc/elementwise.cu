@@ -265,3 +265,99 @@ MYNAH_API int mynah_swiglu(const void* gate_up, void* out, int act_dtype, int T,
         return mynah_fail("swiglu: unsupported activation dtype %d", act_dtype);
     return mynah_check_launch("swiglu");
 }
+
+// ------------------------------------------------- embedding with learned positions
+// x[t, :] = E[token_t, :] + P[position_t, :]        (neither scaled); fp32 sum of the two stored rows
+template <typename TW>
+__global__ void embed_positions_kernel(const TW* __restrict__ table, const TW* __restrict__ pos_table,
+                                       const int* __restrict__ tokens, const int* __restrict__ tok_pos,
+                                       float* __restrict__ x, int D, int V, int n_pos, int* __restrict__ status) {
+    griddep_launch();
+    griddep_wait();
+    const int t = blockIdx.x;
+    const int tok = tokens[t], pos = tok_pos[t];
+    float* out = x + (size_t)t * D;
+    const bool bad_tok = tok < 0 || tok >= V, bad_pos = pos < 0 || pos >= n_pos;
+    if (bad_tok || bad_pos) {
+        if (threadIdx.x == 0) atomicOr(status, bad_tok ? 4 : 2);      // token / position outside its table
+        for (int i = threadIdx.x; i < D; i += blockDim.x) out[i] = 0.f;
+        return;
+    }
+    const TW* row = table + (size_t)tok * D;
+    const TW* prow = pos_table + (size_t)pos * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) out[i] = to_f32(row[i]) + to_f32(prow[i]);
+}
+
+MYNAH_API int mynah_embed_positions(const void* table, const void* pos_table, int table_dtype, const int* tokens,
+                                    const int* tok_pos, float* x, int T, int D, int V, int n_pos, int* status,
+                                    cudaStream_t stream) {
+    if (T == 0) return 0;
+    MYNAH_REQUIRE(T > 0 && D > 0 && V > 0 && n_pos > 0, "embed_positions: bad sizes T=%d D=%d V=%d positions=%d", T, D, V, n_pos);
+    const int threads = D >= 1024 ? 256 : (D >= 256 ? 128 : 64);
+    if (table_dtype == MYNAH_F32)
+        mynah_launch(embed_positions_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table,
+                     (const float*)pos_table, tokens, tok_pos, x, D, V, n_pos, status);
+    else if (table_dtype == MYNAH_BF16)
+        mynah_launch(embed_positions_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)table,
+                     (const bf16*)pos_table, tokens, tok_pos, x, D, V, n_pos, status);
+    else
+        return mynah_fail("embed_positions: unsupported table dtype %d", table_dtype);
+    return mynah_check_launch("embed_positions");
+}
+
+// ------------------------------------------------------------ activations
+// In place or not: out[i] = act(in[i]), computed in fp32. 0: gelu with erf, 0.5 z (1 + erf(z / sqrt 2));
+// 1: gelu with tanh, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 2: silu; 3: relu.
+__device__ __forceinline__ float act_apply(float z, int act) {
+    switch (act) {
+        case 0: return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+        case 1: return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+        case 2: return z / (1.0f + expf(-z));
+        default: return fmaxf(z, 0.f);
+    }
+}
+
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out, long long n, int act) {
+    griddep_launch_small();
+    griddep_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_f32<T>(act_apply(to_f32(in[i]), act));
+}
+
+MYNAH_API int mynah_activation(const void* in, void* out, int dtype, long long n, int act, cudaStream_t stream) {
+    if (n == 0) return 0;
+    MYNAH_REQUIRE(n > 0 && act >= 0 && act <= 3, "activation: bad arguments n=%lld act=%d", n, act);
+    const unsigned blocks = (unsigned)ceil_div_ll(n, 256);
+    if (dtype == MYNAH_F32)
+        mynah_launch(activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)in, (float*)out, n, act);
+    else if (dtype == MYNAH_BF16)
+        mynah_launch(activation_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)in, (bf16*)out, n, act);
+    else
+        return mynah_fail("activation: unsupported dtype %d", dtype);
+    return mynah_check_launch("activation");
+}
+
+// ------------------------------------------------------------------ cast
+// out[i] = in[i] rounded to the activation type: what a sublayer reads of the fp32 residual stream when no
+// norm stands in front of it.
+template <typename T>
+__global__ void cast_f32_kernel(const float* __restrict__ in, T* __restrict__ out, long long n) {
+    griddep_launch_small();
+    griddep_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_f32<T>(in[i]);
+}
+
+MYNAH_API int mynah_cast_f32(const float* in, void* out, int out_dtype, long long n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    MYNAH_REQUIRE(n > 0, "cast_f32: bad size %lld", n);
+    const unsigned blocks = (unsigned)ceil_div_ll(n, 256);
+    if (out_dtype == MYNAH_BF16)
+        mynah_launch(cast_f32_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, in, (bf16*)out, n);
+    else if (out_dtype == MYNAH_F32)
+        mynah_launch(cast_f32_kernel<float>, dim3(blocks), dim3(256), 0, stream, in, (float*)out, n);
+    else
+        return mynah_fail("cast_f32: unsupported dtype %d", out_dtype);
+    return mynah_check_launch("cast_f32");
+}

@@ -1,0 +1,130 @@
+// Short causal convolution along each sequence of a ragged step, one filter per channel.
+//
+//   conv(x)[t, c] = bias[c] + sum_{j=0}^{taps-1} w[c, j] * x[t - (taps-1) + j, c]
+//
+// with zeros before a sequence's first position: the filter's last column weighs the current token. The inputs
+// at the last taps-1 positions of every sequence are carried from step to step in a per-slot state
+// [n_slots + 1][taps-1][C] (fp32; the last row belongs to no sequence and serves padding), so a prompt cut into
+// pieces, or continued token by token, sums the same products in the same order (j ascending) as a prompt run
+// whole. Output: act(conv(x)) or x + act(conv(x)); act: none or silu. All arithmetic is fp32.
+//
+// A step whose sequences bring more than one row reads the old state in the convolution and shifts it in a
+// second launch; a decode step (one row a sequence) does both in one launch, a thread owning its sequence's
+// channel.
+#include "common.cuh"
+
+namespace {
+
+struct ConvArgs {
+    int T, B, C, taps, ldx, ldo, n_slots;
+    int act;          // 0: none, 1: silu
+    int add_input;    // 1: out = x + act(conv(x))
+    int update;       // 1: one row a sequence, shift the state here
+};
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+causal_conv_kernel(const TI* __restrict__ x, VecRef w, VecRef bias, float* __restrict__ state, TO* __restrict__ out,
+                   const int* __restrict__ tok_seq, const int* __restrict__ cu_q, const int* __restrict__ slots,
+                   ConvArgs a) {
+    griddep_launch_small();
+    griddep_wait();
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int row = blockIdx.x;
+    if (c >= a.C) return;
+    const int b = tok_seq[row];
+    TO* o = out + (size_t)row * a.ldo + c;
+    if (b < 0 || b >= a.B) {                       // a padding row
+        *o = from_f32<TO>(0.f);
+        return;
+    }
+    const int i = row - cu_q[b];                   // place of the row in its sequence's piece
+    int slot = slots[b];
+    if (slot < 0 || slot >= a.n_slots) slot = a.n_slots;
+    const int hist = a.taps - 1;
+    float* st = state + (size_t)slot * hist * a.C + c;
+    float acc = bias.p ? bias.at(c) : 0.f;
+    const float cur = to_f32(x[(size_t)row * a.ldx + c]);
+    for (int j = 0; j < a.taps; j++) {
+        const int src = i - hist + j;              // place of the input in the piece; negative: before it
+        float v;
+        if (j == hist) v = cur;
+        else if (src >= 0) v = to_f32(x[(size_t)(row - hist + j) * a.ldx + c]);
+        else v = st[(size_t)(hist + src) * a.C];
+        acc = fmaf(w.at(c * a.taps + j), v, acc);
+    }
+    if (a.act == 1) acc = silu_f(acc);
+    if (a.add_input) acc += cur;
+    *o = from_f32<TO>(acc);
+    if (a.update) {                                // i == 0 and the piece is this row alone
+        for (int k = 0; k + 1 < hist; k++) st[(size_t)k * a.C] = st[(size_t)(k + 1) * a.C];
+        if (hist > 0) st[(size_t)(hist - 1) * a.C] = cur;
+    }
+}
+
+// state[k] <- the input at the piece's place q_len - (taps-1) + k, which lies in the piece or, for a short
+// piece, in the old state at k + q_len (read before any smaller k is written: one thread walks k upwards).
+template <typename TI>
+__global__ void __launch_bounds__(256)
+conv_state_shift_kernel(const TI* __restrict__ x, float* __restrict__ state, const int* __restrict__ cu_q,
+                        const int* __restrict__ slots, ConvArgs a) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.y;
+    if (c >= a.C) return;
+    const int slot = slots[b];
+    if (slot < 0 || slot >= a.n_slots) return;
+    const int q0 = cu_q[b], q_len = cu_q[b + 1] - q0;
+    if (q_len <= 0) return;
+    const int hist = a.taps - 1;
+    float* st = state + (size_t)slot * hist * a.C + c;
+    for (int k = 0; k < hist; k++) {
+        const int src = q_len - hist + k;
+        st[(size_t)k * a.C] = src >= 0 ? to_f32(x[(size_t)(q0 + src) * a.ldx + c]) : st[(size_t)(k + q_len) * a.C];
+    }
+}
+
+template <typename TI, typename TO>
+int launch_conv(const void* x, const VecRef& w, const VecRef& bias, float* state, void* out, const int* tok_seq,
+                const int* cu_q, const int* slots, const ConvArgs& a, cudaStream_t stream) {
+    const int threads = a.C >= 256 ? 256 : (a.C >= 128 ? 128 : 64);
+    const dim3 grid(a.T, ceil_div(a.C, threads));
+    mynah_launch(causal_conv_kernel<TI, TO>, grid, dim3(threads), 0, stream, (const TI*)x, w, bias, state, (TO*)out,
+                 tok_seq, cu_q, slots, a);
+    if (mynah_check_launch("causal_conv")) return -1;
+    if (!a.update && a.taps > 1) {
+        conv_state_shift_kernel<TI><<<dim3(ceil_div(a.C, threads), a.B), threads, 0, stream>>>((const TI*)x, state, cu_q, slots, a);
+        return mynah_check_launch("conv_state_shift");
+    }
+    return 0;
+}
+
+}  // namespace
+
+// x [T, ldx] (x_dtype), w [C, taps] and bias [C] or null (w_dtype), state [n_slots + 1, taps - 1, C] fp32,
+// out [T, ldo] (out_dtype). one_row_each: every sequence of the step brings exactly one row and row b is
+// sequence b (a decode step); the state is then shifted by the same launch.
+MYNAH_API int mynah_causal_conv(const void* x, int x_dtype, int ldx, const void* w, const void* bias, int w_dtype,
+                                float* state, int n_slots, void* out, int out_dtype, int ldo,
+                                const int* tok_seq, const int* cu_q, const int* slots,
+                                int T, int B, int C, int taps, int act, int add_input, int one_row_each,
+                                cudaStream_t stream) {
+    if (T == 0 || C == 0) return 0;
+    MYNAH_REQUIRE(T > 0 && B > 0 && C > 0 && taps >= 1, "causal_conv: bad sizes T=%d B=%d C=%d taps=%d", T, B, C, taps);
+    MYNAH_REQUIRE(ldx >= C && ldo >= C, "causal_conv: a row stride is smaller than the channels");
+    MYNAH_REQUIRE(act == 0 || act == 1, "causal_conv: unknown activation %d", act);
+    MYNAH_REQUIRE(taps == 1 || state != nullptr, "causal_conv: no state given");
+    MYNAH_REQUIRE(B <= 65535 && ceil_div(C, 64) <= 65535, "causal_conv: B=%d or C=%d exceeds one launch", B, C);
+    const ConvArgs a{T, B, C, taps, ldx, ldo, n_slots, act, add_input, one_row_each ? 1 : 0};
+    const VecRef wv{w, w_dtype}, bv{bias, w_dtype};
+    if (x_dtype == MYNAH_F32 && out_dtype == MYNAH_F32)
+        return launch_conv<float, float>(x, wv, bv, state, out, tok_seq, cu_q, slots, a, stream);
+    if (x_dtype == MYNAH_F32 && out_dtype == MYNAH_BF16)
+        return launch_conv<float, bf16>(x, wv, bv, state, out, tok_seq, cu_q, slots, a, stream);
+    if (x_dtype == MYNAH_BF16 && out_dtype == MYNAH_BF16)
+        return launch_conv<bf16, bf16>(x, wv, bv, state, out, tok_seq, cu_q, slots, a, stream);
+    if (x_dtype == MYNAH_BF16 && out_dtype == MYNAH_F32)
+        return launch_conv<bf16, float>(x, wv, bv, state, out, tok_seq, cu_q, slots, a, stream);
+    return mynah_fail("causal_conv: unsupported dtypes %d -> %d", x_dtype, out_dtype);
+}

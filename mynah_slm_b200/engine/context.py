@@ -84,6 +84,9 @@ class StepContext:
     host_q_lens: Optional[list[int]] = None
     host_past: Optional[list[int]] = None
     host_slots: Optional[list[int]] = None
+    # what a part leaves for parts of later layers of the SAME step (values that a later mixer mixes with its
+    # own, say), by a key the parts agree on; on the device, so a captured step carries it along
+    shared: dict = field(default_factory=dict)
 
 
 def device_context(layout: StepLayout, dev_buf: torch.Tensor, n_pages: list[int], max_q_len: int, is_decode: bool,

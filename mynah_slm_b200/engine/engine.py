@@ -341,7 +341,7 @@ class Engine:
         """embedding -> layers in schedule order -> final norm of the wanted
         rows -> head. Returns fp32 logits [rows, vocab]. `taps`, a dictionary,
         receives copies of the residual stream on the way (see `step`)."""
-        x = self.model.embedding.forward(ctx.tokens)
+        x = self._embed(ctx)
         stream = Residual(x)
         if taps is not None:
             taps["embed"] = x.clone()
@@ -496,10 +496,15 @@ class Engine:
         return logits
 
     def _forward_layers_only(self, ctx: StepContext) -> None:
-        x = self.model.embedding.forward(ctx.tokens)
-        stream = Residual(x)
+        stream = Residual(self._embed(ctx))
         for i, e in enumerate(self.model.schedule):
             self.model.layers[e.layer].forward(stream, ctx, self.cache.views[i])
+
+    def _embed(self, ctx: StepContext) -> torch.Tensor:
+        emb = self.model.embedding
+        if getattr(emb, "needs_context", False):       # an embedding that also reads the rows' positions
+            return emb.forward(ctx.tokens, ctx)
+        return emb.forward(ctx.tokens)
 
     def _host_fields(self, ctx: StepContext, entries: Sequence[StepEntry]) -> None:
         ctx.host_q_lens = [len(e.tokens) for e in entries]

@@ -24,7 +24,8 @@ class EntryPlan:
     """Cache of one run of the schedule."""
     group: Optional[int] = None          # storage group of its keys/values
     index_in_group: Optional[int] = None
-    state: Optional[StateRequest] = None
+    state: object = None                 # a StateRequest, or a mapping name -> StateRequest
+    block_state: object = None           # the same, asked for by the layer's block
     source: Optional[int] = None         # schedule index whose cache it reads instead
 
 
@@ -44,7 +45,7 @@ class Model:
         self.layers: list[Block] = []
         for ls in spec.layers:
             mixer = build_part("mixer", ls.mixer)
-            ffn = build_part("ffn", ls.ffn)
+            ffn = build_part("ffn", ls.ffn) if ls.ffn is not None else None
             norms = {k: build_part("norm", v) for k, v in ls.norms.items()}
             self.layers.append(build_part("block", ls.block, mixer, ffn, norms))
         self.schedule = spec.schedule
@@ -73,9 +74,9 @@ class Model:
                                       f"but asks for {kv} where that entry keeps {src_kv}")
                 if st is not None:
                     raise ConfigError(f"schedule[{i}] has state of its own and cannot borrow a cache")
-                plan.entries.append(EntryPlan(source=e.cache_from))
+                plan.entries.append(EntryPlan(source=e.cache_from, block_state=self.layers[e.layer].state_request()))
                 continue
-            ep = EntryPlan(state=st)
+            ep = EntryPlan(state=st, block_state=self.layers[e.layer].state_request())
             if kv is not None:
                 key = (kv.kv_heads, kv.head_dim, kv.window, kv.value_dim)
                 if key not in keys:

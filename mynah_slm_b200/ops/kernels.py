@@ -217,7 +217,8 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
         return _gemv_decode(x, w, N, 0 if out_dtype == torch.bfloat16 else 2, out)
     if isinstance(x, NormedInput):
         x = x.materialize()
-    _chk(x, "linear input", dim=2)
+    if x.dim() != 2 or not x.is_cuda or x.stride(1) != 1:
+        raise KernelError("linear input must be rows on the device (a column slice of a row-major tensor is fine)")
     M, K = x.shape
     N, K2 = w.shape
     if K != K2 or x.dtype != w.dtype:
@@ -227,7 +228,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
             raise KernelError("linear: the 32-bit path writes float32")
         if out is None:
             out = torch.empty((M, N), dtype=torch.float32, device=x.device)
-        call("mynah_gemm_f32", ptr(x), ptr(w), ptr(out), M, N, K, K, K, N, stream_ptr())
+        call("mynah_gemm_f32", ptr(x), ptr(w), ptr(out), M, N, K, x.stride(0) if M > 1 else K, K, N, stream_ptr())
         return out
     if x.dtype != torch.bfloat16:
         raise KernelError(f"linear: unsupported dtype {x.dtype}")
@@ -507,3 +508,236 @@ def l2_prefetch(tensors) -> None:
         ptrs = (ctypes.c_void_p * len(part))(*[t.data_ptr() for t in part])
         sizes = (ctypes.c_ulonglong * len(part))(*[t.numel() * t.element_size() for t in part])
         call("mynah_l2_prefetch", ptrs, sizes, len(part), stream_ptr())
+
+
+# ------------------------------------------------------------------ parts of mixers with recurrent state
+ACTIVATIONS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+def embed_positions(table: torch.Tensor, pos_table: torch.Tensor, tokens: torch.Tensor, tok_pos: torch.Tensor,
+                    status: torch.Tensor) -> torch.Tensor:
+    """x[t] = table[token_t] + pos_table[position_t], fp32 [T, D]."""
+    _chk(table, "embedding table", dim=2)
+    _chk(pos_table, "position table", table.dtype, 2)
+    _chk(tokens, "tokens", torch.int32, 1)
+    _chk(tok_pos, "positions", torch.int32, 1)
+    T, (V, D) = tokens.numel(), table.shape
+    if pos_table.shape[1] != D:
+        raise KernelError("embed_positions: the two tables differ in width")
+    out = torch.empty((T, D), dtype=torch.float32, device=table.device)
+    call("mynah_embed_positions", ptr(table), ptr(pos_table), code(table.dtype), ptr(tokens), ptr(tok_pos), ptr(out),
+         T, D, V, pos_table.shape[0], ptr(status), stream_ptr())
+    return out
+
+
+def activation(x: torch.Tensor, act: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = act(x) elementwise (fp32 arithmetic); `out` may be x itself."""
+    _chk(x, "activation input")
+    if act not in ACTIVATIONS:
+        raise KernelError(f"unknown activation {act!r}; known: {', '.join(sorted(ACTIVATIONS))}")
+    if out is None:
+        out = torch.empty_like(x)
+    call("mynah_activation", ptr(x), ptr(out), code(x.dtype), x.numel(), ACTIVATIONS[act], stream_ptr())
+    return out
+
+
+def cast_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The fp32 residual rows rounded to the activation type."""
+    _chk(x, "residual", torch.float32)
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    call("mynah_cast_f32", ptr(x), ptr(out), code(dtype), x.numel(), stream_ptr())
+    return out
+
+
+def layernorm_rows(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float, act_dtype: torch.dtype,
+                   rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """LN(x[rows]) * w + b of the fp32 residual stream, in the activation type."""
+    _chk(x, "residual", torch.float32, 2)
+    _chk(w, "norm weight", dim=1)
+    if b is not None:
+        _chk(b, "norm bias", w.dtype, 1)
+    D = x.shape[1]
+    if w.numel() != D or (b is not None and b.numel() != D):
+        raise KernelError("layernorm: weight or bias does not match the row")
+    n = x.shape[0]
+    if rows is not None:
+        _chk(rows, "rows", torch.int32, 1)
+        n = rows.numel()
+    out = torch.empty((n, D), dtype=act_dtype, device=x.device)
+    call("mynah_layernorm_rows", ptr(x), ptr(rows), ptr(w), ptr(b), code(w.dtype), ptr(out), code(act_dtype), n, D,
+         float(eps), stream_ptr())
+    return out
+
+
+def layernorm_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float,
+                  copy: bool = False) -> Optional[torch.Tensor]:
+    """x += LN(y) * w + b, row by row (x fp32, in place). With `copy` the new x is also returned in y's type."""
+    _chk(x, "residual", torch.float32, 2)
+    if y.dim() != 2 or y.stride(1) != 1 or not y.is_cuda:
+        raise KernelError("layernorm_add: the sublayer's output must be rows on the device")
+    if y.shape != x.shape:
+        raise KernelError(f"layernorm_add: output {tuple(y.shape)} does not match the residual {tuple(x.shape)}")
+    _chk(w, "norm weight", dim=1)
+    if b is not None:
+        _chk(b, "norm bias", w.dtype, 1)
+    n, D = x.shape
+    xc = torch.empty((n, D), dtype=y.dtype, device=x.device) if copy else None
+    call("mynah_layernorm_add", ptr(y), code(y.dtype), y.stride(0), ptr(w), ptr(b), code(w.dtype), ptr(x), ptr(xc),
+         n, D, float(eps), stream_ptr())
+    return xc
+
+
+def causal_conv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: Optional[torch.Tensor],
+                ctx, out_dtype: torch.dtype, act: Optional[str] = None, add_input: bool = False,
+                channels: Optional[int] = None) -> torch.Tensor:
+    """Per-channel causal convolution along each sequence of the step (see csrc/seq_conv.cu). x [T, >= C] rows
+    (a column slice is fine), w [C, taps], state fp32 [max_seqs + 1, taps - 1, C]: read, then shifted."""
+    if x.dim() != 2 or x.stride(1) != 1 or not x.is_cuda:
+        raise KernelError("causal_conv: the input must be rows on the device")
+    _chk(w, "filter", dim=2)
+    C, taps = w.shape
+    if channels is not None and channels != C:
+        raise KernelError("causal_conv: the filter does not match the channels")
+    if x.shape[1] != C:
+        raise KernelError(f"causal_conv: the input has {x.shape[1]} channels, the filter {C}")
+    if bias is not None:
+        _chk(bias, "filter bias", w.dtype, 1)
+    if taps > 1:
+        _chk(state, "convolution state", torch.float32, 3)
+        if tuple(state.shape[1:]) != (taps - 1, C):
+            raise KernelError(f"causal_conv: state rows are {tuple(state.shape[1:])}, expected {(taps - 1, C)}")
+    if act not in (None, "silu"):
+        raise KernelError(f"causal_conv: activation {act!r} is not built in (none or 'silu')")
+    T = x.shape[0]
+    out = torch.empty((T, C), dtype=out_dtype, device=x.device)
+    call("mynah_causal_conv", ptr(x), code(x.dtype), x.stride(0), ptr(w), ptr(bias), code(w.dtype),
+         ptr(state), (state.shape[0] - 1) if state is not None else 0, ptr(out), code(out_dtype), C,
+         ptr(ctx.tok_seq), ptr(ctx.cu_q), ptr(ctx.slots), T, ctx.B, C, taps, 1 if act == "silu" else 0,
+         1 if add_input else 0, 1 if ctx.is_decode else 0, stream_ptr())
+    return out
+
+
+def attn_prep(qkv: torch.Tensor, q_out: torch.Tensor, H: int, G: int, dim: int, vd: int, dimp: int, vdp: int,
+              q_gain: torch.Tensor, k_gain: torch.Tensor, eps: float, cos, sin, rot: int, ctx, pages: PageTableView,
+              k_cache, v_cache, v_first: Optional[torch.Tensor], lam: Optional[torch.Tensor], vmix: int) -> None:
+    """Whole-projection q/k norm, partial rotation, per-head value norm, value mixing, cache write (csrc/attn_prep.cu)."""
+    _chk(qkv, "qkv", dim=2)
+    _chk(q_out, "q", qkv.dtype, 2)
+    if q_gain.dtype != k_gain.dtype or q_gain.numel() != H * dim or k_gain.numel() != G * dim:
+        raise KernelError("attn_prep: the gains must cover the whole q and k projections, in one dtype")
+    if k_cache is not None:
+        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
+            raise KernelError("attn_prep: the cache and the activations differ in dtype")
+        if tuple(k_cache.shape[1:]) != (G, PAGE_TOKENS, dimp) or tuple(v_cache.shape[1:]) != (G, PAGE_TOKENS, vdp):
+            raise KernelError("attn_prep: the cache pages do not have the stored head sizes")
+    if qkv.shape[1] < H * dim + (G * (dim + vd) if k_cache is not None else 0):
+        raise KernelError("attn_prep: the projection's rows are too short")
+    if v_first is not None:
+        _chk(v_first, "v_first", torch.float32, 2)
+        if v_first.shape[0] < qkv.shape[0] or v_first.shape[1] != G * vd:
+            raise KernelError("attn_prep: v_first does not match the step")
+    if lam is not None:
+        _chk(lam, "mixing weight", torch.float32)
+    n_pos = cos.shape[0] if cos is not None else 0
+    call("mynah_attn_prep", ptr(qkv), code(qkv.dtype), qkv.shape[0], qkv.shape[1], ptr(q_out), q_out.shape[1],
+         H, G, dim, vd, dimp, vdp, ptr(q_gain), ptr(k_gain), code(q_gain.dtype), float(eps),
+         ptr(cos), ptr(sin), rot, n_pos, ptr(ctx.tok_seq), ptr(ctx.tok_pos),
+         ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages,
+         ptr(k_cache), ptr(v_cache), ptr(v_first), ptr(lam), vmix, ptr(ctx.status), stream_ptr())
+
+
+def attn_prefill_general(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, VD: int,
+                         k_cache: torch.Tensor, v_cache: torch.Tensor, pages: PageTableView,
+                         window: int, chunk: int, scale: float) -> None:
+    """The general prompt attention with value heads of their own width, a given score scale and a chunk mask."""
+    _chk(q, "q", dim=2)
+    _chk(out, "attention output", q.dtype, 2)
+    call("mynah_attn_prefill_generic_ex", ptr(q), ptr(out), code(q.dtype), q.shape[0], ctx.B, ctx.max_q_len, H, KV, HD, VD,
+         q.shape[1], out.shape[1], ptr(k_cache), ptr(v_cache), ptr(ctx.cu_q), ptr(ctx.kv_len),
+         ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages, window or 0, chunk or 0, float(scale),
+         ptr(ctx.status), stream_ptr())
+
+
+def attn_decode_general(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, VD: int,
+                        k_cache: torch.Tensor, v_cache: torch.Tensor, pages: PageTableView,
+                        window: int, chunk: int, scale: float, scratch: torch.Tensor) -> None:
+    _chk(q, "q", dim=2)
+    _chk(out, "attention output", q.dtype, 2)
+    _chk(scratch, "scratch", torch.float32)
+    need = ctx.B * H * ctx.decode_splits * (VD + 2)
+    if scratch.numel() < need:
+        raise KernelError(f"attn_decode: scratch holds {scratch.numel()} floats, {need} are needed")
+    call("mynah_attn_decode_ex", ptr(q), ptr(out), code(q.dtype), ctx.B, H, KV, HD, VD, q.shape[1], out.shape[1],
+         ptr(k_cache), ptr(v_cache), ptr(ctx.kv_len), ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages,
+         window or 0, chunk or 0, float(scale), ctx.decode_splits, ptr(scratch), ptr(ctx.status), stream_ptr())
+
+
+def _rows(t: torch.Tensor, name: str) -> None:
+    if t.dim() != 2 or t.stride(1) != 1 or not t.is_cuda:
+        raise KernelError(f"{name} must be rows on the device (unit stride along a row)")
+
+
+def selective_scan(x: torch.Tensor, z: torch.Tensor, dt_raw: torch.Tensor, Bm: torch.Tensor, Cm: torch.Tensor,
+                   dt_bias, A_log: torch.Tensor, D, state: torch.Tensor, ctx) -> torch.Tensor:
+    """The Mamba-1 recurrence with its gate (csrc/selective_scan.cu). x, z [T, inner] (z may be a column slice);
+    dt_raw [T, inner], Bm, Cm [T, N] column slices of one tensor; state fp32 [max_seqs + 1, inner, N]."""
+    for t, n in ((x, "x"), (z, "z"), (dt_raw, "dt"), (Bm, "B"), (Cm, "C")):
+        _rows(t, "selective_scan: " + n)
+    _chk(state, "scan state", torch.float32, 3)
+    T, inner = x.shape
+    N = A_log.shape[1]
+    if tuple(state.shape[1:]) != (inner, N) or Bm.shape[1] != N or Cm.shape[1] != N or Bm.stride(0) != Cm.stride(0):
+        raise KernelError("selective_scan: sizes do not fit")
+    if z.dtype != x.dtype or Bm.dtype != Cm.dtype or dt_raw.dtype != torch.float32:
+        raise KernelError("selective_scan: dtypes do not fit (dt in float32, B and C alike, z like x)")
+    if A_log.dtype != dt_bias.dtype or A_log.dtype != D.dtype:
+        raise KernelError("selective_scan: A_log, dt bias and D must share a dtype")
+    y = torch.empty((T, inner), dtype=x.dtype, device=x.device)
+    call("mynah_selective_scan", ptr(x), x.stride(0), ptr(z), z.stride(0), ptr(y), inner, code(x.dtype),
+         ptr(dt_raw), dt_raw.stride(0), ptr(Bm), ptr(Cm), Bm.stride(0), code(Bm.dtype),
+         ptr(dt_bias), ptr(A_log), ptr(D), code(A_log.dtype), ptr(state), state.shape[0] - 1,
+         ptr(ctx.cu_q), ptr(ctx.slots), ctx.B, inner, N, stream_ptr())
+    return y
+
+
+def delta_prep(qk: torch.Tensor, a_raw: torch.Tensor, b_raw: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor,
+               H: int, G: int, dim: int):
+    """Unit q and k per head, beta and the decay of the gated delta rule (csrc/delta_rule.cu); all fp32."""
+    for t, n in ((qk, "q|k"), (a_raw, "a"), (b_raw, "b")):
+        _rows(t, "delta_prep: " + n)
+    if a_raw.stride(0) != b_raw.stride(0) or a_raw.dtype != qk.dtype or b_raw.dtype != qk.dtype:
+        raise KernelError("delta_prep: a and b must be column slices of one tensor of the activations' type")
+    T = qk.shape[0]
+    dev = qk.device
+    qn = torch.empty((T, G * dim), dtype=torch.float32, device=dev)
+    kn = torch.empty((T, G * dim), dtype=torch.float32, device=dev)
+    g = torch.empty((T, H), dtype=torch.float32, device=dev)
+    beta = torch.empty((T, H), dtype=torch.float32, device=dev)
+    call("mynah_delta_prep", ptr(qk), qk.stride(0), ptr(a_raw), ptr(b_raw), a_raw.stride(0), code(qk.dtype),
+         ptr(A_log), ptr(dt_bias), code(A_log.dtype), ptr(qn), ptr(kn), ptr(g), ptr(beta), T, H, G, dim, stream_ptr())
+    return qn, kn, g, beta
+
+
+def delta_rule(qn: torch.Tensor, kn: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
+               state: torch.Tensor, ctx, H: int, G: int, dim: int, vd: int) -> torch.Tensor:
+    """The recurrence; state fp32 [max_seqs + 1, H, dim, vd]; returns o fp32 [T, H * vd]."""
+    _rows(v, "delta_rule: v")
+    _chk(state, "delta state", torch.float32, 4)
+    if tuple(state.shape[1:]) != (H, dim, vd):
+        raise KernelError("delta_rule: the state does not fit")
+    T = v.shape[0]
+    o = torch.empty((T, H * vd), dtype=torch.float32, device=v.device)
+    call("mynah_delta_rule", ptr(qn), ptr(kn), ptr(v), v.stride(0), code(v.dtype), ptr(g), ptr(beta), ptr(state),
+         state.shape[0] - 1, ptr(o), ptr(ctx.cu_q), ptr(ctx.slots), ctx.B, H, G, dim, vd, stream_ptr())
+    return o
+
+
+def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, H: int, vd: int, eps: float) -> torch.Tensor:
+    """o / rms(o per head) * w * silu(gate); o fp32 [T, H * vd], gate rows in the activation type."""
+    _chk(o, "o", torch.float32, 2)
+    _rows(gate, "gated_rmsnorm: gate")
+    T = o.shape[0]
+    out = torch.empty((T, H * vd), dtype=gate.dtype, device=o.device)
+    call("mynah_gated_rmsnorm", ptr(o), ptr(gate), gate.stride(0), code(gate.dtype), ptr(w), code(w.dtype), ptr(out),
+         T, H, vd, float(eps), stream_ptr())
+    return out

@@ -85,6 +85,25 @@ _SIGNATURES: dict[str, list] = {
     "mynah_wait_probe": [P, P, ctypes.c_ulonglong, P],
     "mynah_read_probe": [P, P, c_int, c_int, c_int, P, P, P],
     "mynah_randn_fill": [P, c_int, c_longlong, ctypes.c_ulonglong, ctypes.c_ulonglong, c_double, c_double, P],
+    "mynah_embed_positions": [P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, P, P],
+    "mynah_activation": [P, P, c_int, c_longlong, c_int, P],
+    "mynah_cast_f32": [P, P, c_int, c_longlong, P],
+    "mynah_layernorm_rows": [P, P, P, P, c_int, P, c_int, c_int, c_int, c_float, P],
+    "mynah_layernorm_add": [P, c_int, c_int, P, P, c_int, P, P, c_int, c_int, c_float, P],
+    "mynah_causal_conv": [P, c_int, c_int, P, P, c_int, P, c_int, P, c_int, c_int, P, P, P,
+                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, P],
+    "mynah_attn_prep": [P, c_int, c_int, c_int, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                        P, P, c_int, c_float, P, P, c_int, c_int, P, P, P, P, P, c_int,
+                        P, P, P, P, c_int, P, P],
+    "mynah_attn_prefill_generic_ex": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                      P, P, P, P, P, P, P, c_int, c_int, c_int, c_float, P, P],
+    "mynah_attn_decode_ex": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                             P, P, P, P, P, P, c_int, c_int, c_int, c_float, c_int, P, P, P],
+    "mynah_selective_scan": [P, c_int, P, c_int, P, c_int, c_int, P, c_int, P, P, c_int, c_int,
+                             P, P, P, c_int, P, c_int, P, P, c_int, c_int, c_int, P],
+    "mynah_delta_prep": [P, c_int, P, P, c_int, c_int, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, P],
+    "mynah_delta_rule": [P, P, P, c_int, c_int, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
+    "mynah_gated_rmsnorm": [P, P, c_int, c_int, P, c_int, P, c_int, c_int, c_int, c_float, P],
 }
 
 

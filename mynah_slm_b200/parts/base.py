@@ -95,13 +95,17 @@ class CacheView:
        `slot` belongs to the sequence in that slot; the last row belongs to no
        sequence: rows of a step that are padding (slot -1) may read and write
        it, so that a part can index with `where(slots >= 0, slots, max_seqs)`
-       on the device and run from a captured graph.
+       on the device and run from a captured graph. A mixer that asked for
+       several states by name gets a dictionary of such tensors.
+    block_state: the same for the state that the layer's block asked for (a
+       dictionary by name), or None.
     """
     group: Optional[int] = None
     k: Optional[torch.Tensor] = None
     v: Optional[torch.Tensor] = None
     writes: bool = True
-    state: Optional[torch.Tensor] = None
+    state: Any = None
+    block_state: Any = None
 
 
 # ------------------------------------------------------------------- parts
@@ -155,7 +159,9 @@ class Mixer(Part):
     def kv_request(self) -> Optional[KVRequest]:
         return None
 
-    def state_request(self) -> Optional[StateRequest]:
+    def state_request(self):
+        """None, one `StateRequest`, or a mapping name -> `StateRequest` (a mixer with a recurrent state and the
+        tails of its short convolutions, say); `cache.state` then has the same form."""
         return None
 
     def forward(self, h: torch.Tensor, ctx: "Any", cache: CacheView) -> torch.Tensor:
@@ -190,7 +196,12 @@ class Block(Part):
         self.mixer, self.ffn, self.norms = mixer, ffn, dict(norms)
 
     def parts(self) -> list[Part]:
-        return [self.mixer, self.ffn, *self.norms.values()]
+        return [p for p in (self.mixer, self.ffn, *self.norms.values()) if p is not None]
+
+    def state_request(self):
+        """Per-sequence state of the block itself (not its mixer's): None or a mapping name -> `StateRequest`;
+        it arrives as `cache.block_state`."""
+        return None
 
     def forward(self, stream: "Residual", ctx: "Any", cache: CacheView) -> None:
         raise NotImplementedError

@@ -59,3 +59,29 @@ class LinearHead(Head):
 
 register_embedding("token_embedding", TokenEmbedding)
 register_head("linear_head", LinearHead)
+
+
+class TokenPositionEmbedding(Embedding):
+    """x = E[token] + P[position]: a learned vector per absolute position, added unscaled to the token's.
+    Parameters: name, position_name, vocab_size, dim, max_positions. It reads the rows' positions, so the
+    engine hands it the step's context."""
+    needs_context = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.name, self.pos_name = str(spec["name"]), str(spec["position_name"])
+        self.V, self.D, self.P = int(spec["vocab_size"]), int(spec["dim"]), int(spec["max_positions"])
+        self.table: Optional[torch.Tensor] = None
+        self.pos_table: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [TensorSpec(self.name, (self.V, self.D)), TensorSpec(self.pos_name, (self.P, self.D))]
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], runtime) -> None:
+        self.table, self.pos_table = tensors[self.name], tensors[self.pos_name]
+
+    def forward(self, tokens: torch.Tensor, ctx) -> torch.Tensor:
+        return kernels.embed_positions(self.table, self.pos_table, tokens, ctx.tok_pos, ctx.status)
+
+
+register_embedding("token_position_embedding", TokenPositionEmbedding)

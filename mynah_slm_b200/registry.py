@@ -48,8 +48,11 @@ def known_architectures() -> list[str]:
 
 def architecture_of(config: Mapping[str, Any]) -> Architecture:
     archs = config.get("architectures")
+    if archs is None and isinstance(config.get("architecture"), str):
+        archs = [config["architecture"]]          # some designs name their class in a single string
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("missing config key: architectures (a list with the model class name)")
+        raise ConfigError("missing config key: architectures (a list with the model class name), "
+                          "or architecture (its name)")
     if archs[0] not in _ARCHITECTURES:
         raise ConfigError(f"unknown architecture {archs[0]!r}; known: {', '.join(known_architectures())}")
     return _ARCHITECTURES[archs[0]]
@@ -81,6 +84,8 @@ def read_config_folder(folder: str) -> TypedConfig:
 def _register_builtin() -> None:
     from .config.qwen3 import ARCHITECTURE, Qwen3Config
     register_architecture(ARCHITECTURE, Qwen3Config.from_dict, replace=True)
+    from .config import supisun
+    register_architecture(supisun.ARCHITECTURE, supisun.SupisunConfig.from_dict, replace=True)
 
 
 _register_builtin()
