@@ -5,6 +5,7 @@ and 64.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --workload 4b|8b      (the two larger workloads, a JSON line of their own each)
+    python bench.py --design supisun      (the Supisun design beside Qwen3 at equal size, a JSON line of its own)
 
 One JSON line on stdout. A step is one decode step of the batch.
   value     decoded tokens per second, timed on the device with CUDA events
@@ -292,6 +293,99 @@ def time_reader() -> int:
     return 0
 
 
+# The Supisun design at layer sizes that resemble a real model's, beside Qwen3 at equal width, depth, feed-forward
+# width, heads and vocabulary. Its layers repeat (mamba1, attention, delta, attention); the attention layers keep the
+# Qwen3 shape's heads, with a chunk of 1,024 positions and value mixing.
+def supisun_config(shape: str, layers: int) -> dict:
+    c = dict(QWEN3_0_6B)
+    c.update(SHAPES[shape])
+    D, H, G, HD, F = c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"], c["intermediate_size"]
+    mlp = {"kind": "dense", "ff": F}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": H, "kv_heads": G, "dim": HD, "vdim": HD, "scale": HD ** -0.5, "rot": {"dims": HD, "base": 1e6},
+                     "mask": {"size": 1024}, "v_mix": True}}
+    mam = {"type": "mamba1", "mlp": mlp, "mixer": {"inner": 2 * D, "state": 16, "dt_rank": D // 16, "conv": 4}}
+    dlt = {"type": "delta", "mlp": mlp, "mixer": {"heads": H, "kv_heads": G, "dim": HD, "vdim": HD, "conv": 4}}
+    pattern = [mam, att, dlt, att]
+    return {"architecture": "Supisun", "vocab": c["vocab_size"], "width": D, "max_positions": 8192, "norm": {"eps": 1e-6},
+            "canon": {"taps": 3}, "layers": [pattern[i % 4] for i in range(layers)]}
+
+
+def run_design(args) -> int:
+    """`--design supisun`: prefill of one 2,048-token prompt and decode steps at --batch behind 2,048-token prompts, for
+    the design and for Qwen3 at equal size (`--model` runs one of the two: for a launch list of that model alone)."""
+    import numpy as np
+    import torch
+
+    from mynah_slm_b200 import LLM
+    from mynah_slm_b200.engine.engine import StepEntry
+    from mynah_slm_b200.ops import lib
+    from mynah_slm_b200.sampling.sampler import SamplingParams
+
+    K, W, B, T = args.steps, max(3, args.warmup), args.batch, args.prompt_len
+    out = {"design": args.design, "batch": B, "prompt_len": T, "steps": K, "dtype": "bf16", "data": "random weights", "shapes": {}}
+    rng = np.random.default_rng(3)
+    for shape in ([args.shape] if args.only else ["0.6b", "4b"]):
+        q = dict(QWEN3_0_6B)
+        q.update(SHAPES[shape])
+        q["max_position_embeddings"] = 8192
+        layers = args.layers or q["num_hidden_layers"]
+        q["num_hidden_layers"] = layers
+        res = {"layers": layers}
+        for name, cfg in (("supisun", supisun_config(shape, layers)), ("qwen3", q)):
+            if args.model and args.model != name:
+                continue
+            V = cfg.get("vocab", cfg.get("vocab_size"))
+            llm = LLM.random(cfg, seed=2, dtype="bfloat16", max_tokens=B * (T + 2 * (K + W) + 128), max_seqs=B)
+            eng = llm.engine
+            eng.sampler.set_params(SamplingParams.greedy())
+            r = {}
+            if args.only in ("", "prefill"):
+                p = rng.integers(0, V, size=T).tolist()
+                times = []
+                for i in range(3 + 5):
+                    s = eng.open_sequence()
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    eng.step([StepEntry(s, p, (T - 1,))])
+                    e1.record()
+                    torch.cuda.synchronize()
+                    eng.close_sequence(s)
+                    if i >= 3:
+                        times.append(e0.elapsed_time(e1))
+                ms = statistics.median(times)
+                r["prefill_ms"], r["prefill_tokens_per_s"] = round(ms, 3), round(T / (ms / 1e3), 1)
+            if args.only in ("", "decode"):
+                for rep in range(2):                    # the first batch captures the steps, the second is timed
+                    prompts = [rng.integers(0, V, size=T).tolist() for _ in range(B)]
+                    slots = [eng.open_sequence() for _ in range(B)]
+                    eng.sampler.start_sequences(slots, list(range(1, B + 1)), prompts)
+                    logits = eng.step([StepEntry(s, p, (T - 1,)) for s, p in zip(slots, prompts)])
+                    first = eng.sampler.sample(logits, torch.tensor(slots, dtype=torch.int32, device=eng.device)).cpu().tolist()
+                    toks = eng.decode_loop(slots, first, W)[:B].cpu().tolist()
+                    torch.cuda.synchronize()
+                    n0 = lib.launch_count()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    eng.decode_loop(slots, toks, K)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ms = e0.elapsed_time(e1)
+                    launches = lib.launch_count() - n0
+                    eng.check_status()
+                    for s in slots:
+                        eng.close_sequence(s)
+                r["decode_ms_per_step"], r["decode_tokens_per_s"] = round(ms / K, 4), round(B * K / (ms / 1e3), 1)
+                r["launches_per_step"] = launches // K
+            res[name] = r
+            del llm, eng
+            torch.cuda.empty_cache()
+        out["shapes"][shape] = res
+    print(json.dumps(out))
+    return 0
+
+
 def run_reference(args) -> int:
     """The unmodified reference on the same metric: 8 requests with 2,048-token prompts, one after another (it has
     no batch), token by token (prompts too), on the host's CPU cores (it has no GPU path). See baseline/reference_arm.py."""
@@ -345,6 +439,9 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of the decode phases")
     ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes, for --only runs (the full line is always 0.6b)")
     ap.add_argument("--workload", default="", choices=["", "4b", "8b"], help="run one of the two larger workloads instead")
+    ap.add_argument("--design", default="", choices=["", "supisun"],
+                    help="measure this design beside Qwen3 at equal size instead (prefill and decode; a line of its own)")
+    ap.add_argument("--model", default="", choices=["", "supisun", "qwen3"], help="with --design: only this one of the two")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -363,6 +460,8 @@ def main() -> int:
     from mynah_slm_b200.ops import gemm_bf16, lib
     from mynah_slm_b200.sampling.sampler import SamplingParams
 
+    if args.design:
+        return run_design(args)
     if args.workload:
         return run_workload(args.workload, args.layers)
     if args.only == "products":

@@ -51,9 +51,17 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// The first key that a sequence's newest position (hi - 1) sees. `window` carries either bound: W > 0 keeps the last
+// W positions; -C < 0 is a chunk mask, keys from floor((hi - 1) / C) * C on; 0: every key.
+__device__ __forceinline__ int first_visible(int hi, int window) {
+    if (window > 0) return max(0, hi - window);
+    if (window < 0 && hi > 0) return ((hi - 1) / -window) * -window;
+    return 0;
+}
+
 struct TcArgs {
     int H, KV, ldq;
-    int window, S;
+    int window, S;          // window: see first_visible
     float scale;
 };
 
@@ -97,7 +105,7 @@ __device__ __forceinline__ PageJob page_job(int s, int g, int b, const int* __re
     j.s = s; j.g = g; j.b = b; j.page = -1; j.k_first = 0; j.k_last = -1;
     const int G = a.H / a.KV;
     const int hi = kv_len[b];
-    const int lo = a.window > 0 ? max(0, hi - a.window) : 0;
+    const int lo = first_visible(hi, a.window);
     int key_begin = 0, key_end = 0;
     if (hi > 0) {
         const int pg0 = lo / PAGE_TOKENS, pg1 = (hi - 1) / PAGE_TOKENS + 1;
@@ -362,7 +370,7 @@ attn_decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cac
         __syncthreads();
         if (!last_flag) return;
         const int hi = kv_len[b];
-        const int lo = a.window > 0 ? max(0, hi - a.window) : 0;
+        const int lo = first_visible(hi, a.window);
         const int n_vis = hi > 0 ? min(a.S, (hi - 1) / PAGE_TOKENS + 1 - lo / PAGE_TOKENS) : 0;
         merge_pages<HD>(part_o, part_ml, out + (size_t)b * ldo + (size_t)g * G * HD, ((size_t)b * a.H + (size_t)g * G) * a.S,
                         G, a.S, n_vis, reinterpret_cast<float*>(k_s), reinterpret_cast<float*>(v_s), red_m[0]);
@@ -466,7 +474,7 @@ attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restri
     griddep_wait();
     griddep_launch_small();
     const int hi = kv_len[b];
-    const int lo = window > 0 ? max(0, hi - window) : 0;
+    const int lo = first_visible(hi, window);
     const int n_vis = hi > 0 ? min(S, (hi - 1) / PAGE_TOKENS + 1 - lo / PAGE_TOKENS) : 0;
     merge_pages<HD>(part_o, part_ml, out + (size_t)b * ldo + (size_t)h * HD, ((size_t)b * H + h) * S, 1, S, n_vis, w_s, acc_s, inv_s);
 }
@@ -513,7 +521,7 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, VecRef q_gain, VecRef k_g
     griddep_launch();
     griddep_wait();
     const int hi = kv_len[b];
-    const int lo = a.window > 0 ? max(0, hi - a.window) : 0;
+    const int lo = first_visible(hi, a.window);
     const int pos = hi > 0 ? tok_pos[b] : 0;
     int key_begin = 0, key_end = 0, page = -1, n_vis = 0, mp = 0;
     if (hi > 0) {
@@ -693,7 +701,7 @@ attn_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
     griddep_wait();
     for (int b = tid; b < B; b += STREAM_THREADS) {
         const int hi = kv_len[b];
-        const int lo = a.window > 0 ? max(0, hi - a.window) : 0;
+        const int lo = first_visible(hi, a.window);
         int n = 0;
         if (hi > 0) {
             n = (hi - 1) / PAGE_TOKENS + 1 - lo / PAGE_TOKENS;
@@ -890,17 +898,37 @@ MYNAH_API int mynah_attn_decode_tc_supported(int H, int KV, int HD) {
 // Same arguments and scratch layout as mynah_attn_decode; bfloat16 only. `counters`: B * KV words that are zero
 // before the first call (every call leaves them zero), or null: with them the pages' kernel also merges, by the
 // CTA that finishes a (sequence, kv head) last; without them the merge is a second launch. The result is the same.
+MYNAH_API int mynah_attn_decode_tc_ex(
+    const void* q, void* out, int B, int H, int KV, int HD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int chunk, float scale, int n_splits, float* scratch, unsigned* counters, int* status, cudaStream_t stream);
+
 MYNAH_API int mynah_attn_decode_tc(
     const void* q, void* out, int B, int H, int KV, int HD, int ldq, int ldo,
     const void* k_cache, const void* v_cache, const int* kv_len,
     const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
     int window, int n_splits, float* scratch, unsigned* counters, int* status, cudaStream_t stream) {
+    MYNAH_REQUIRE(window >= 0, "attn_decode_tc: negative window");
+    return mynah_attn_decode_tc_ex(q, out, B, H, KV, HD, ldq, ldo, k_cache, v_cache, kv_len, page_indptr, page_ids, page_base,
+                                   n_pages, window, 0, 0.f, n_splits, scratch, counters, status, stream);
+}
+
+// The same with a chunk mask instead of the window (one of the two, 0: none) and a score scale given by the caller
+// (0: 1/sqrt(HD)).
+MYNAH_API int mynah_attn_decode_tc_ex(
+    const void* q, void* out, int B, int H, int KV, int HD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window_in, int chunk, float scale, int n_splits, float* scratch, unsigned* counters, int* status, cudaStream_t stream) {
     if (B == 0) return 0;
+    MYNAH_REQUIRE(window_in >= 0 && chunk >= 0 && !(window_in > 0 && chunk > 0), "attn_decode_tc: a window or a chunk, not both");
+    const int window = chunk > 0 ? -chunk : window_in;
     MYNAH_REQUIRE(mynah_attn_decode_tc_supported(H, KV, HD), "attn_decode_tc: H=%d KV=%d head_dim=%d is not taken by this kernel", H, KV, HD);
     MYNAH_REQUIRE(ldq % 8 == 0, "attn_decode_tc: query row stride %d must be a multiple of 8", ldq);
     MYNAH_REQUIRE(n_splits >= 1 && n_splits <= 65535 && B <= 65535 && KV <= 65535, "attn_decode_tc: launch too large");
     MYNAH_REQUIRE(scratch != nullptr, "attn_decode_tc: no scratch memory given");
-    const TcArgs a{H, KV, ldq, window, n_splits, 1.0f / sqrtf((float)HD)};
+    const TcArgs a{H, KV, ldq, window, n_splits, scale != 0.f ? scale : 1.0f / sqrtf((float)HD)};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)B * H * n_splits * HD;

@@ -46,7 +46,16 @@ constexpr int HALF_BYTES = 128 * 128; // 128 rows of 128 bytes: one 64-column ha
 struct PfArgs {
     int B, H, KV, ldo;
     int window;
-    float scale_log2;                 // (1 / sqrt(head_dim)) * log2(e)
+    float scale_log2;                 // (1 / sqrt(head_dim)) * log2(e), or the caller's scale * log2(e)
+    int chunk;                        // 0: none; C: the row at position p sees keys from floor(p / C) * C on
+    // The first key that the row at position p sees. Window and chunk both give a bound that does not fall as p
+    // grows, so a tile's first row has the tile's lowest bound and its last row the highest.
+    __device__ __forceinline__ bool bounded() const { return window > 0 || chunk > 0; }
+    __device__ __forceinline__ int row_lo(int p) const {
+        int lo = window > 0 ? max(0, p - window + 1) : 0;
+        if (chunk > 0) lo = max(lo, (p / chunk) * chunk);
+        return lo;
+    }
 };
 
 // With -DMYNAH_ATTN_STAMPS the CTA of head 0 that walks the most key tiles writes its SM's cycle counter at fixed
@@ -140,9 +149,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int kvl = kv_len[b], past = kvl - n_q;
     const int rows_valid = min(BQ, n_q - q0);
     const int kt_hi = (past + q0 + rows_valid - 1) / BKV;      // tile of the last key that the last row sees
-    const int kt_lo = a.window > 0 ? max(0, past + q0 - a.window + 1) / BKV : 0;
+    const int kt_lo = a.bounded() ? a.row_lo(past + q0) / BKV : 0;
     const int n_tiles = kt_hi - kt_lo + 1;
-    const int lo_min = a.window > 0 ? max(0, past + q0 - a.window + 1) : 0;    // the first key that any row of the tile sees
+    const int lo_min = a.bounded() ? a.row_lo(past + q0) : 0;    // the first key that any row of the tile sees
     const int kvh = h / (a.H / a.KV);
 #ifdef MYNAH_ATTN_STAMPS
     const bool stamp_on = blockIdx.x == 0 && blockIdx.y == 0;
@@ -289,7 +298,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const int qpos = past + q0 + row;
-        const int lo_r = a.window > 0 ? max(0, qpos - a.window + 1) : 0;
+        const int lo_r = a.bounded() ? a.row_lo(qpos) : 0;
+        const bool bounded = a.bounded();
+        const int lo_max = bounded ? a.row_lo(past + q0 + BQ - 1) : 0;    // the highest bound of any row of the tile
         const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16);
         const uint32_t t_o = t_row + O_COL + grp * (HD / 2);   // this thread's half of the row of O
         constexpr int HALF_KEYS = BKV / 2;
@@ -308,14 +319,14 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             STAMP(j, 1);
             // does any row of the tile have a key, among this group's, that it must not see?
             const bool need_mask = key0 + HALF_KEYS - 1 > past + q0 || key0 + HALF_KEYS > kvl ||
-                                   (a.window > 0 && key0 < past + q0 + BQ - a.window);
+                                   (bounded && key0 < lo_max);
             const int hi = min(qpos, kvl - 1) - key0;          // the last of this thread's scores that its row sees
-            const int lo = a.window > 0 ? lo_r - key0 : -(1 << 30);
+            const int lo = bounded ? lo_r - key0 : -(1 << 30);
             // 32 of the thread's scores (the c-th half of them), those that the row must not see set to -inf
             auto fetch32 = [&](int c, float (&v)[32]) {
                 tc_ld32(t_s + grp * HALF_KEYS + c * 32, reinterpret_cast<uint32_t(&)[32]>(v));
                 if (need_mask) {                               // a compare with a constant and a select per score
-                    if (a.window > 0) {
+                    if (bounded) {
 #pragma unroll
                         for (int e = 0; e < 32; e++) v[e] = (c * 32 + e <= hi && c * 32 + e >= lo) ? v[e] : -INFINITY;
                     } else {
@@ -333,7 +344,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (int c = 0; c < HALF_KEYS / 32; c++) tc_wait_ld(reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
                 STAMP(j, 2);
                 if (need_mask) {
-                    if (a.window > 0) {
+                    if (bounded) {
 #pragma unroll
                         for (int e = 0; e < HALF_KEYS; e++) s[e] = (e <= hi && e >= lo) ? s[e] : -INFINITY;
                     } else {
@@ -541,12 +552,29 @@ MYNAH_API int mynah_attn_prefill_tcgen05_supported(int H, int KV, int HD) {
 
 // q: [n_tokens, ldq] bf16 with head h in columns [h * HD, (h + 1) * HD); out: [n_tokens, ldo]; the cache tensors
 // are [n_pages, KV, 64, HD] bf16. Otherwise the arguments of mynah_attn_prefill_generic.
+MYNAH_API int mynah_attn_prefill_tcgen05_ex(
+    const void* q, void* out, int n_tokens, int B, int max_q_len, int H, int KV, int HD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* cu_q, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int chunk, float scale, int* status, cudaStream_t stream);
+
 MYNAH_API int mynah_attn_prefill_tcgen05(
     const void* q, void* out, int n_tokens, int B, int max_q_len, int H, int KV, int HD, int ldq, int ldo,
     const void* k_cache, const void* v_cache, const int* cu_q, const int* kv_len,
     const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
     int window, int* status, cudaStream_t stream) {
+    return mynah_attn_prefill_tcgen05_ex(q, out, n_tokens, B, max_q_len, H, KV, HD, ldq, ldo, k_cache, v_cache, cu_q, kv_len,
+                                         page_indptr, page_ids, page_base, n_pages, window, 0, 0.f, status, stream);
+}
+
+// The same with a chunk mask beside the window (0: none) and a score scale given by the caller (0: 1/sqrt(HD)).
+MYNAH_API int mynah_attn_prefill_tcgen05_ex(
+    const void* q, void* out, int n_tokens, int B, int max_q_len, int H, int KV, int HD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* cu_q, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int chunk, float scale, int* status, cudaStream_t stream) {
     if (B == 0 || max_q_len == 0 || n_tokens == 0) return 0;
+    MYNAH_REQUIRE(window >= 0 && chunk >= 0, "attn_prefill_tcgen05: negative window or chunk");
     MYNAH_REQUIRE(mynah_attn_prefill_tcgen05_supported(H, KV, HD), "attn_prefill_tcgen05: H=%d KV=%d head_dim=%d is not taken by this kernel", H, KV, HD);
     MYNAH_REQUIRE(ldq % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
                   ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0,
@@ -557,7 +585,7 @@ MYNAH_API int mynah_attn_prefill_tcgen05(
     if (make_map(&mq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n_tokens, (long long)H * HD, ldq, BQ, 64)) return -1;
     if (make_map(&mk, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)n_pages * KV * PAGE_TOKENS, HD, HD, PAGE_TOKENS, 64)) return -1;
     if (make_map(&mv, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)n_pages * KV * PAGE_TOKENS, HD, HD, PAGE_TOKENS, 64)) return -1;
-    const PfArgs a{B, H, KV, ldo, window, (1.0f / sqrtf((float)HD)) * 1.4426950408889634f};
+    const PfArgs a{B, H, KV, ldo, window, (scale != 0.f ? scale : 1.0f / sqrtf((float)HD)) * 1.4426950408889634f, chunk};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
     // Two CTAs an SM pay once there are several waves of CTAs (64 prompts of 2,048 tokens and 32 heads: 2.97 against
     // 3.34 ms; 4 prompts: 221 against 236 us); with one wave or two, the longest CTA's own chain sets the time and it

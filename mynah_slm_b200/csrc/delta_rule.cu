@@ -9,8 +9,10 @@
 //                 beta = sigmoid(b_raw);  g = exp(-exp(A_log_h) * softplus(a_raw + dt_bias_h))       (fp32 out)
 //   delta_rule    the recurrence. The columns of S are independent given k, q, g and beta, so a CTA takes a
 //                 tile of columns of one head of one sequence; a column's dim values are spread over L adjacent
-//                 lanes (at most 32 values a lane, in registers) that add their parts of the two dot products
-//                 by shuffles in a fixed order. S is fp32 [n_slots + 1][H][dim][vd], carried per slot.
+//                 lanes (about 16 values a lane, in registers) that add their parts of the two dot products
+//                 by shuffles in a fixed order. Sixteen tokens' keys, queries, values, decays and betas are
+//                 staged in shared memory at a time, so that the chain from token to token waits on no load
+//                 from global memory. S is fp32 [n_slots + 1][H][dim][vd], carried per slot.
 //   gated_rmsnorm out = o / rms(o over the head's vd) * w[d] * silu(gate)
 //
 // All arithmetic is fp32. A sequence's rows are walked in order, so a prompt run whole, in pieces or token by
@@ -57,69 +59,116 @@ delta_prep_kernel(const T* __restrict__ qk, const T* __restrict__ a_raw, const T
 }
 
 constexpr int DELTA_THREADS = 128;
-constexpr int DELTA_R = 32;                 // state values a lane
+constexpr int DELTA_TB = 16;                // tokens staged in shared memory at a time
 
 struct DeltaArgs {
     int B, H, G, dim, vd, n_slots, ldv;
-    int L;                                   // lanes a column
+    int L;                                   // lanes a column (a power of two)
+    int per;                                 // key values a lane: ceil(dim / L) rounded up to a multiple of 4
 };
 
-template <typename T>
+// Keys and queries of a staged token lie in shared memory lane chunk by lane chunk: `per` values, then zeros up to
+// RMAX (what a lane reads), then 4 unused floats, so that the L lanes of a column read their chunks (as 16-byte
+// vectors) from different banks.
+__device__ __forceinline__ int kq_slot(int i, int per, int stride) { return (i / per) * stride + i % per; }
+
+template <typename T, int RMAX>
 __global__ void __launch_bounds__(DELTA_THREADS)
 delta_rule_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const T* __restrict__ v,
                   const float* __restrict__ g, const float* __restrict__ beta, float* __restrict__ state,
                   float* __restrict__ o, const int* __restrict__ cu_q, const int* __restrict__ slots, DeltaArgs a) {
+    extern __shared__ float sm[];
     griddep_wait();
     const int b = blockIdx.z, h = blockIdx.y;
     const int slot = slots[b];
     const int q0 = cu_q[b], q1 = cu_q[b + 1];
     if (slot < 0 || slot >= a.n_slots || q1 <= q0) return;
-    const int L = a.L;
-    const int l = threadIdx.x % L;
-    const int j = blockIdx.x * (DELTA_THREADS / L) + threadIdx.x / L;
+    const int L = a.L, per = a.per;
+    const int JT = DELTA_THREADS / L;                            // columns of this CTA
+    const int l = threadIdx.x % L, jl = threadIdx.x / L;
+    const int j = blockIdx.x * JT + jl;
     const bool on = j < a.vd;
     const int jj = on ? j : a.vd - 1;
     const int kvh = h / (a.H / a.G);
+    constexpr int CS = RMAX + 4;                                 // floats of a lane's chunk
+    const int row = CS * L;                                      // floats of a staged key (or query)
+    float* ks = sm;                                              // [TB][row]
+    float* qs = ks + DELTA_TB * row;                             // [TB][row]
+    float* vs = qs + DELTA_TB * row;                             // [TB][JT]
+    float* os = vs + DELTA_TB * JT;                              // [TB][JT]
+    float* gs = os + DELTA_TB * JT;                              // [TB] decay, [TB] beta
+    for (int i = threadIdx.x; i < 2 * DELTA_TB * row; i += DELTA_THREADS) ks[i] = 0.f;      // the unused slots stay zero
 
-    float S[DELTA_R];
+    float S[RMAX];
     float* st = state + (((size_t)slot * a.H + h) * a.dim) * a.vd + jj;
+    const int i0 = l * per;
 #pragma unroll
-    for (int r = 0; r < DELTA_R; r++) {
-        const int i = l + r * L;
-        S[r] = i < a.dim ? st[(size_t)i * a.vd] : 0.f;
-    }
-    for (int t = q0; t < q1; t++) {
-        const float* kt = kn + ((size_t)t * a.G + kvh) * a.dim;
-        const float* qt = qn + ((size_t)t * a.G + kvh) * a.dim;
-        const float gt = g[(size_t)t * a.H + h], bt = beta[(size_t)t * a.H + h];
-        const float vt = to_f32(v[(size_t)t * a.ldv + (size_t)h * a.vd + jj]);
-        float kr[DELTA_R];
-        float dot = 0.f;
-#pragma unroll
-        for (int r = 0; r < DELTA_R; r++) {
-            const int i = l + r * L;
-            kr[r] = i < a.dim ? kt[i] : 0.f;
-            S[r] *= gt;
-            dot = fmaf(S[r], kr[r], dot);
+    for (int r = 0; r < RMAX; r++) S[r] = (r < per && i0 + r < a.dim) ? st[(size_t)(i0 + r) * a.vd] : 0.f;
+
+    for (int t0 = q0; t0 < q1; t0 += DELTA_TB) {
+        const int nt = min(DELTA_TB, q1 - t0);
+        __syncthreads();                                         // the block before is consumed (and the zeroing done)
+        for (int idx = threadIdx.x; idx < nt * a.dim; idx += DELTA_THREADS) {
+            const int tt = idx / a.dim, i = idx % a.dim;
+            const size_t src = ((size_t)(t0 + tt) * a.G + kvh) * a.dim + i;
+            ks[tt * row + kq_slot(i, per, CS)] = kn[src];
+            qs[tt * row + kq_slot(i, per, CS)] = qn[src];
         }
-        for (int s = L >> 1; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
-        const float u = bt * (vt - dot);
-        float out = 0.f;
-#pragma unroll
-        for (int r = 0; r < DELTA_R; r++) {
-            const int i = l + r * L;
-            S[r] = fmaf(kr[r], u, S[r]);
-            out = fmaf(S[r], i < a.dim ? qt[i] : 0.f, out);
+        for (int idx = threadIdx.x; idx < nt * JT; idx += DELTA_THREADS) {
+            const int tt = idx / JT, c = idx % JT;
+            const int col = blockIdx.x * JT + c;
+            vs[idx] = col < a.vd ? to_f32(v[(size_t)(t0 + tt) * a.ldv + (size_t)h * a.vd + col]) : 0.f;
         }
-        for (int s = L >> 1; s > 0; s >>= 1) out += __shfl_xor_sync(0xffffffffu, out, s);
-        if (on && l == 0) o[(size_t)t * a.H * a.vd + (size_t)h * a.vd + j] = out;
+        if (threadIdx.x < nt) {
+            gs[threadIdx.x] = g[(size_t)(t0 + threadIdx.x) * a.H + h];
+            gs[DELTA_TB + threadIdx.x] = beta[(size_t)(t0 + threadIdx.x) * a.H + h];
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; tt++) {
+            const float gt = gs[tt], bt = gs[DELTA_TB + tt];
+            const float4* k4 = reinterpret_cast<const float4*>(ks + tt * row + l * CS);
+            const float4* q4 = reinterpret_cast<const float4*>(qs + tt * row + l * CS);
+            float kr[RMAX];
+            float dot = 0.f;
+#pragma unroll
+            for (int r = 0; r < RMAX; r += 4) {
+                const float4 kk = k4[r >> 2];
+                kr[r] = kk.x; kr[r + 1] = kk.y; kr[r + 2] = kk.z; kr[r + 3] = kk.w;
+            }
+#pragma unroll
+            for (int r = 0; r < RMAX; r++) {
+                S[r] *= gt;
+                dot = fmaf(S[r], kr[r], dot);
+            }
+            for (int s = L >> 1; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
+            const float u = bt * (vs[tt * JT + jl] - dot);
+            float out = 0.f;
+#pragma unroll
+            for (int r = 0; r < RMAX; r += 4) {
+                const float4 qq = q4[r >> 2];
+                S[r] = fmaf(kr[r], u, S[r]);
+                S[r + 1] = fmaf(kr[r + 1], u, S[r + 1]);
+                S[r + 2] = fmaf(kr[r + 2], u, S[r + 2]);
+                S[r + 3] = fmaf(kr[r + 3], u, S[r + 3]);
+                out = fmaf(S[r], qq.x, out);
+                out = fmaf(S[r + 1], qq.y, out);
+                out = fmaf(S[r + 2], qq.z, out);
+                out = fmaf(S[r + 3], qq.w, out);
+            }
+            for (int s = L >> 1; s > 0; s >>= 1) out += __shfl_xor_sync(0xffffffffu, out, s);
+            if (l == 0) os[tt * JT + jl] = out;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * JT; idx += DELTA_THREADS) {
+            const int tt = idx / JT, c = idx % JT;
+            const int col = blockIdx.x * JT + c;
+            if (col < a.vd) o[(size_t)(t0 + tt) * a.H * a.vd + (size_t)h * a.vd + col] = os[idx];
+        }
     }
     if (on) {
 #pragma unroll
-        for (int r = 0; r < DELTA_R; r++) {
-            const int i = l + r * L;
-            if (i < a.dim) st[(size_t)i * a.vd] = S[r];
-        }
+        for (int r = 0; r < RMAX; r++)
+            if (r < per && i0 + r < a.dim) st[(size_t)(i0 + r) * a.vd] = S[r];
     }
 }
 
@@ -177,20 +226,31 @@ MYNAH_API int mynah_delta_rule(const float* qn, const float* kn, const void* v, 
                                cudaStream_t stream) {
     if (B == 0) return 0;
     MYNAH_REQUIRE(B > 0 && H > 0 && G > 0 && dim > 0 && vd > 0 && H % G == 0, "delta_rule: bad sizes B=%d H=%d G=%d dim=%d vd=%d", B, H, G, dim, vd);
-    MYNAH_REQUIRE(dim <= 32 * DELTA_R, "delta_rule: a key of %d values exceeds %d", dim, 32 * DELTA_R);
+    MYNAH_REQUIRE(dim <= 1024, "delta_rule: a key of %d values exceeds 1024", dim);
     MYNAH_REQUIRE(B <= 65535 && H <= 65535, "delta_rule: B=%d or H=%d exceeds one launch", B, H);
     int L = 1;
-    while (L * DELTA_R < dim) L <<= 1;
-    const DeltaArgs a{B, H, G, dim, vd, n_slots, ldv, L};
-    const dim3 grid(ceil_div(vd, DELTA_THREADS / L), H, B);
-    if (dtype == MYNAH_F32)
-        mynah_launch(delta_rule_kernel<float>, grid, dim3(DELTA_THREADS), 0, stream, qn, kn, (const float*)v, g, beta, state, o,
-                     cu_q, slots, a);
-    else if (dtype == MYNAH_BF16)
-        mynah_launch(delta_rule_kernel<bf16>, grid, dim3(DELTA_THREADS), 0, stream, qn, kn, (const bf16*)v, g, beta, state, o,
-                     cu_q, slots, a);
-    else
-        return mynah_fail("delta_rule: unsupported dtype %d", dtype);
+    while (L * 16 < dim && L < 32) L <<= 1;                     // about 16 key values a lane
+    const int per = (ceil_div(dim, L) + 3) / 4 * 4;
+    const DeltaArgs a{B, H, G, dim, vd, n_slots, ldv, L, per};
+    const int JT = DELTA_THREADS / L;
+    const dim3 grid(ceil_div(vd, JT), H, B);
+    const int rmax = per <= 16 ? 16 : 32;
+    const size_t smem = sizeof(float) * ((size_t)2 * DELTA_TB * (rmax + 4) * L + (size_t)2 * DELTA_TB * JT + 2 * DELTA_TB);
+#define DELTA_LAUNCH(T, RMAX)                                                                                          \
+    if (smem > 48 * 1024 &&                                                                                            \
+        cudaFuncSetAttribute(delta_rule_kernel<T, RMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+        return mynah_fail("delta_rule: %zu bytes of shared memory are not to be had", smem);                          \
+    mynah_launch(delta_rule_kernel<T, RMAX>, grid, dim3(DELTA_THREADS), smem, stream, qn, kn, (const T*)v, g, beta, state, o, \
+                 cu_q, slots, a)
+    if (dtype != MYNAH_F32 && dtype != MYNAH_BF16) return mynah_fail("delta_rule: unsupported dtype %d", dtype);
+    if (rmax == 16) {
+        if (dtype == MYNAH_F32) { DELTA_LAUNCH(float, 16); }
+        else { DELTA_LAUNCH(bf16, 16); }
+    } else {
+        if (dtype == MYNAH_F32) { DELTA_LAUNCH(float, 32); }
+        else { DELTA_LAUNCH(bf16, 32); }
+    }
+#undef DELTA_LAUNCH
     return mynah_check_launch("delta_rule");
 }
 

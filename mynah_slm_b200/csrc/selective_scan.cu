@@ -9,7 +9,7 @@
 // S is fp32 [n_slots + 1][inner][N], carried from step to step per slot (the last row belongs to no sequence).
 // Everything here is fp32 arithmetic; x, B, C and z are read in the type the projections left them in, dt_raw is fp32.
 //
-// A channel's N state values are spread over NL adjacent lanes (NL a power of two, N / NL <= 8 values a lane in
+// A channel's N state values are spread over NL adjacent lanes (NL a power of two, 8 consecutive values a lane in
 // registers), which add their parts of the read-out by shuffles in a fixed order. A CTA takes one sequence and
 // 128 / NL channels and walks the sequence's rows in order, so a prompt run whole, in pieces or token by token
 // performs the same operations in the same order.
@@ -19,6 +19,7 @@ namespace {
 
 constexpr int SCAN_THREADS = 128;
 constexpr int SCAN_R = 8;                     // state values a lane
+constexpr int SCAN_TB = 32;                   // tokens staged in shared memory at a time
 
 struct ScanArgs {
     int B, inner, N, n_slots;
@@ -28,60 +29,99 @@ struct ScanArgs {
 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
+// Thirty-two tokens at a time are staged in shared memory: the CTA's channels of x and of the step size (softplus
+// applied on the way in), and the tokens' B and C, each lane's SCAN_R values followed by 4 unused floats so that the
+// lanes of a channel read 16-byte vectors from different banks. The chain from token to token then waits on no
+// load from global memory; y = (S.C + D x) silu(z) goes back through shared memory, so that z is read and y written
+// in whole rows.
 template <typename TX, typename TD>
 __global__ void __launch_bounds__(SCAN_THREADS)
 selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt_raw, VecRef dt_bias, VecRef A_log, VecRef Dv,
                       const TD* __restrict__ Bm, const TD* __restrict__ Cm, const TX* __restrict__ z,
                       float* __restrict__ state, TX* __restrict__ y,
                       const int* __restrict__ cu_q, const int* __restrict__ slots, ScanArgs a) {
+    extern __shared__ float sm[];
     griddep_wait();
     const int b = blockIdx.y;
     const int slot = slots[b];
     const int q0 = cu_q[b], q1 = cu_q[b + 1];
     if (slot < 0 || slot >= a.n_slots || q1 <= q0) return;
     const int NL = a.NL;
-    const int l = threadIdx.x % NL;
-    const int c = blockIdx.x * (SCAN_THREADS / NL) + threadIdx.x / NL;
+    const int CB = SCAN_THREADS / NL;             // channels of this CTA
+    const int l = threadIdx.x % NL, cl = threadIdx.x / NL;
+    const int c0 = blockIdx.x * CB;
+    const int c = c0 + cl;
     const bool on = c < a.inner;
     const int cc = on ? c : a.inner - 1;          // lanes past the last channel compute and store nothing
+    constexpr int CS = SCAN_R + 4;
+    const int brow = CS * NL;
+    float* xs = sm;                               // [TB][CB]
+    float* ds = xs + SCAN_TB * CB;                // [TB][CB] step sizes
+    float* ys = ds + SCAN_TB * CB;                // [TB][CB]
+    float* bs = ys + SCAN_TB * CB;                // [TB][brow]
+    float* cs = bs + SCAN_TB * brow;              // [TB][brow]
+    for (int i = threadIdx.x; i < 2 * SCAN_TB * brow; i += SCAN_THREADS) bs[i] = 0.f;
 
     float S[SCAN_R], A[SCAN_R];
     float* st = state + ((size_t)slot * a.inner + cc) * a.N;
 #pragma unroll
     for (int r = 0; r < SCAN_R; r++) {
-        const int n = l + r * NL;
+        const int n = l * SCAN_R + r;
         S[r] = n < a.N ? st[n] : 0.f;
         A[r] = n < a.N ? -expf(A_log.at(cc * a.N + n)) : 0.f;
     }
-    const float bias = dt_bias.p ? dt_bias.at(cc) : 0.f;
     const float Dc = Dv.p ? Dv.at(cc) : 0.f;
 
-    for (int t = q0; t < q1; t++) {
-        const float xv = to_f32(x[(size_t)t * a.ldx + cc]);
-        const float dt = softplus_f(dt_raw[(size_t)t * a.lddt + cc] + bias);
-        const float dx = dt * xv;
-        const TD* Bt = Bm + (size_t)t * a.ldbc;
-        const TD* Ct = Cm + (size_t)t * a.ldbc;
-        float acc = 0.f;
-#pragma unroll
-        for (int r = 0; r < SCAN_R; r++) {
-            const int n = l + r * NL;
-            if (n < a.N) {
-                S[r] = fmaf(expf(dt * A[r]), S[r], dx * to_f32(Bt[n]));
-                acc = fmaf(S[r], to_f32(Ct[n]), acc);
-            }
+    for (int t0 = q0; t0 < q1; t0 += SCAN_TB) {
+        const int nt = min(SCAN_TB, q1 - t0);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * CB; idx += SCAN_THREADS) {
+            const int tt = idx / CB, ch = c0 + idx % CB;
+            const bool ok = ch < a.inner;
+            xs[idx] = ok ? to_f32(x[(size_t)(t0 + tt) * a.ldx + ch]) : 0.f;
+            ds[idx] = ok ? softplus_f(dt_raw[(size_t)(t0 + tt) * a.lddt + ch] + (dt_bias.p ? dt_bias.at(ch) : 0.f)) : 0.f;
         }
-        for (int o = NL >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (on && l == 0) {
-            const float zv = to_f32(z[(size_t)t * a.ldz + c]);
-            const float out = (acc + Dc * xv) * (zv / (1.0f + expf(-zv)));
-            y[(size_t)t * a.ldy + c] = from_f32<TX>(out);
+        for (int idx = threadIdx.x; idx < nt * a.N; idx += SCAN_THREADS) {
+            const int tt = idx / a.N, n = idx % a.N;
+            const int at = tt * brow + (n / SCAN_R) * CS + n % SCAN_R;
+            bs[at] = to_f32(Bm[(size_t)(t0 + tt) * a.ldbc + n]);
+            cs[at] = to_f32(Cm[(size_t)(t0 + tt) * a.ldbc + n]);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; tt++) {
+            const float xv = xs[tt * CB + cl], dt = ds[tt * CB + cl];
+            const float dx = dt * xv;
+            const float4* b4 = reinterpret_cast<const float4*>(bs + tt * brow + l * CS);
+            const float4* c4 = reinterpret_cast<const float4*>(cs + tt * brow + l * CS);
+            float acc = 0.f;
+#pragma unroll
+            for (int r = 0; r < SCAN_R; r += 4) {
+                const float4 bb = b4[r >> 2], cv = c4[r >> 2];
+                S[r] = fmaf(expf(dt * A[r]), S[r], dx * bb.x);
+                S[r + 1] = fmaf(expf(dt * A[r + 1]), S[r + 1], dx * bb.y);
+                S[r + 2] = fmaf(expf(dt * A[r + 2]), S[r + 2], dx * bb.z);
+                S[r + 3] = fmaf(expf(dt * A[r + 3]), S[r + 3], dx * bb.w);
+                acc = fmaf(S[r], cv.x, acc);
+                acc = fmaf(S[r + 1], cv.y, acc);
+                acc = fmaf(S[r + 2], cv.z, acc);
+                acc = fmaf(S[r + 3], cv.w, acc);
+            }
+            for (int o = NL >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (l == 0) ys[tt * CB + cl] = acc + Dc * xv;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * CB; idx += SCAN_THREADS) {
+            const int tt = idx / CB, ch = c0 + idx % CB;
+            if (ch < a.inner) {
+                const float zv = to_f32(z[(size_t)(t0 + tt) * a.ldz + ch]);
+                y[(size_t)(t0 + tt) * a.ldy + ch] = from_f32<TX>(ys[idx] * (zv / (1.0f + expf(-zv))));
+            }
         }
     }
     if (on) {
 #pragma unroll
         for (int r = 0; r < SCAN_R; r++) {
-            const int n = l + r * NL;
+            const int n = l * SCAN_R + r;
             if (n < a.N) st[n] = S[r];
         }
     }
@@ -106,12 +146,16 @@ MYNAH_API int mynah_selective_scan(const void* x, int ldx, const void* z, int ld
     const ScanArgs a{B, inner, N, n_slots, ldx, lddt, ldbc, ldz, ldy, NL};
     const VecRef bias{dt_bias, w_dtype}, al{A_log, w_dtype}, dv{Dv, w_dtype};
     const dim3 grid(ceil_div(inner, SCAN_THREADS / NL), B);
+    const size_t smem = sizeof(float) * ((size_t)3 * SCAN_TB * (SCAN_THREADS / NL) + (size_t)2 * SCAN_TB * (SCAN_R + 4) * NL);
 #define SCAN_LAUNCH(TX, TD)                                                                                              \
-    mynah_launch(selective_scan_kernel<TX, TD>, grid, dim3(SCAN_THREADS), 0, stream, (const TX*)x, dt_raw, bias, al, \
+    if (smem > 48 * 1024 &&                                                                                              \
+        cudaFuncSetAttribute(selective_scan_kernel<TX, TD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+        return mynah_fail("selective_scan: %zu bytes of shared memory are not to be had", smem);                        \
+    mynah_launch(selective_scan_kernel<TX, TD>, grid, dim3(SCAN_THREADS), smem, stream, (const TX*)x, dt_raw, bias, al, \
                  dv, (const TD*)Bm, (const TD*)Cm, (const TX*)z, state, (TX*)y, cu_q, slots, a)
-    if (act_dtype == MYNAH_F32 && proj_dtype == MYNAH_F32) SCAN_LAUNCH(float, float);
-    else if (act_dtype == MYNAH_BF16 && proj_dtype == MYNAH_F32) SCAN_LAUNCH(bf16, float);
-    else if (act_dtype == MYNAH_BF16 && proj_dtype == MYNAH_BF16) SCAN_LAUNCH(bf16, bf16);
+    if (act_dtype == MYNAH_F32 && proj_dtype == MYNAH_F32) { SCAN_LAUNCH(float, float); }
+    else if (act_dtype == MYNAH_BF16 && proj_dtype == MYNAH_F32) { SCAN_LAUNCH(bf16, float); }
+    else if (act_dtype == MYNAH_BF16 && proj_dtype == MYNAH_BF16) { SCAN_LAUNCH(bf16, bf16); }
     else return mynah_fail("selective_scan: unsupported dtypes %d, %d", act_dtype, proj_dtype);
 #undef SCAN_LAUNCH
     return mynah_check_launch("selective_scan");

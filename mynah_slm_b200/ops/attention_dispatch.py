@@ -82,3 +82,29 @@ def decode(qkv: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, 
     else:
         kernels.attn_decode(qkv, out, ctx.B, H, KV, HD, k_cache, v_cache, ctx.kv_len, pages, window,
                             ctx.decode_splits, scratch, ctx.status)
+
+
+# Switch for the tensor-core kernels under mixers with a chunk mask or a scale of their own (tests compare them with
+# the general kernels).
+USE_TC_MASKED = os.environ.get("MYNAH_TC_MASKED_ATTN", "1") != "0"
+
+
+def prefill_masked(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, VD: int, k_cache, v_cache, pages,
+                   window: int, chunk: int, scale: float) -> None:
+    """Prompt attention for mixers with a chunk mask, a score scale of their own or value heads of another width:
+    the tcgen05 kernel where it takes the sizes (bfloat16, keys and values of one width, 64 or 128, a positive
+    scale), else the general kernel. Both give the same result up to rounding."""
+    if (USE_TC_MASKED and USE_TCGEN05_PREFILL and HD == VD and scale > 0.0 and kernels.attn_prefill_tcgen05_supported(q.dtype, H, KV, HD)):
+        kernels.attn_prefill_tcgen05_masked(q, out, ctx, H, KV, HD, k_cache, v_cache, pages, window, chunk, scale)
+        return
+    kernels.attn_prefill_general(q, out, ctx, H, KV, HD, VD, k_cache, v_cache, pages, window, chunk, scale)
+
+
+def decode_masked(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, VD: int, k_cache, v_cache, pages,
+                  window: int, chunk: int, scale: float, scratch: torch.Tensor) -> None:
+    """The same choice for a decode step (the tensor-core kernel takes a window or a chunk, not both)."""
+    if (USE_TC_MASKED and HD == VD and not (window and chunk) and kernels.attn_decode_tc_supported(q.dtype, H, KV, HD)
+            and _tc_fits(H, KV, ctx.decode_splits)):
+        kernels.attn_decode_tc_masked(q, out, ctx, H, KV, HD, k_cache, v_cache, pages, window, chunk, scale, scratch)
+        return
+    kernels.attn_decode_general(q, out, ctx, H, KV, HD, VD, k_cache, v_cache, pages, window, chunk, scale, scratch)

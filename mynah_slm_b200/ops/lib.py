@@ -95,6 +95,10 @@ _SIGNATURES: dict[str, list] = {
     "mynah_attn_prep": [P, c_int, c_int, c_int, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                         P, P, c_int, c_float, P, P, c_int, c_int, P, P, P, P, P, c_int,
                         P, P, P, P, c_int, P, P],
+    "mynah_attn_prefill_tcgen05_ex": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                      P, P, P, P, P, P, P, c_int, c_int, c_int, c_float, P, P],
+    "mynah_attn_decode_tc_ex": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P, P, P, P, P, c_int,
+                                c_int, c_int, c_float, c_int, P, P, P, P],
     "mynah_attn_prefill_generic_ex": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                       P, P, P, P, P, P, P, c_int, c_int, c_int, c_float, P, P],
     "mynah_attn_decode_ex": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,

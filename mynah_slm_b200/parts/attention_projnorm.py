@@ -132,13 +132,14 @@ class ProjNormAttention(Mixer):
                           self.rot, ctx, pages, cache.k if writes else None, cache.v if writes else None,
                           v_first, self.lam, vmix)
         out = torch.empty((T, H * vdp), dtype=qkv.dtype, device=qkv.device)
+        from ..ops import attention_dispatch
         if ctx.is_decode:
-            kernels.attn_decode_general(q, out, ctx, H, G, dimp, vdp, cache.k, cache.v, pages, self.window or 0,
-                                        self.chunk or 0, self.scale,
-                                        self.runtime.attn_scratch(ctx.B, H, vdp, ctx.decode_splits))
+            attention_dispatch.decode_masked(q, out, ctx, H, G, dimp, vdp, cache.k, cache.v, pages, self.window or 0,
+                                             self.chunk or 0, self.scale,
+                                             self.runtime.attn_scratch(ctx.B, H, vdp, ctx.decode_splits))
         else:
-            kernels.attn_prefill_general(q, out, ctx, H, G, dimp, vdp, cache.k, cache.v, pages, self.window or 0,
-                                         self.chunk or 0, self.scale)
+            attention_dispatch.prefill_masked(q, out, ctx, H, G, dimp, vdp, cache.k, cache.v, pages, self.window or 0,
+                                              self.chunk or 0, self.scale)
         return kernels.linear(out, self.w_o)
 
 

@@ -103,7 +103,17 @@ SHARP = config(64, 150, [
     with_mlp(attn(2, 1, 32, 16, 0.8, rot=(8, 50.0), mask=130, v_mix=True), None),
 ], taps=2, max_positions=600)
 
-CONFIGS = {"hybrid": HYBRID, "odd": ODD, "attention": ONLY_ATTENTION, "mamba": ONLY_MAMBA, "delta": ONLY_DELTA,
+# heads of 64 and 128 with keys and values alike: the sizes the tensor-core attention kernels take in bfloat16;
+# chunks that are no multiple of a page or of a tile, a large state and wide keys in the recurrent layers
+WIDE = config(128, 200, [
+    with_mlp(attn(4, 2, 64, 64, 0.125, rot=(64, 10000.0), mask=100, v_mix=True), 128),
+    with_mlp(attn(2, 1, 128, 128, 0.09, rot=(32, 500.0), mask=150), None),
+    with_mlp(mamba(160, 40, 8, 4), None),
+    with_mlp(delta(2, 1, 136, 24, 2), None),
+    with_mlp(attn(4, 2, 64, 64, 0.2, mask=200, v_mix=True), 96),
+], taps=2, max_positions=700)
+
+CONFIGS = {"wide": WIDE, "hybrid": HYBRID, "odd": ODD, "attention": ONLY_ATTENTION, "mamba": ONLY_MAMBA, "delta": ONLY_DELTA,
            "mlp": ONLY_MLP, "sharp": SHARP}
 
 
@@ -371,6 +381,29 @@ def test_every_position_across_edges_sharp(models):
                 if L["mixer"]["mask"]["size"] == size:
                     L["mixer"]["mask"]["size"] = size + off
             assert rel_err(ref, plain.forward(other, W, toks)) > 100 * FP32_TOL, f"control: chunk {size}{off:+d} goes unseen"
+
+
+def test_tensor_core_attention_under_chunks(models):
+    """bfloat16 with heads of 64 and 128: the tensor-core kernels with chunk mask and given scale against the plain
+    implementation, and against the general kernels on the same cache, whole, in pieces and decoded."""
+    from mynah_slm_b200.ops import attention_dispatch
+    _, cfg, W = models["wide"]
+    toks = tokens_for(cfg, 520, 41)
+    ref = plain.forward(cfg, W, toks)
+    eng = engine(models, "wide", "bfloat16")
+    runs = {}
+    for use_tc in (True, False):
+        attention_dispatch.USE_TC_MASKED = use_tc
+        try:
+            eng_k = eng if use_tc else engine(models, "wide", "bfloat16", use_graphs=False)
+            runs[use_tc] = [run_pieces(eng_k, toks, cuts) for cuts in ([], [99, 100, 101, 128, 150, 200, 201, 300, 399, 400],
+                                                                       range(380, 520))]
+        finally:
+            attention_dispatch.USE_TC_MASKED = True
+    for got_tc, got_general in zip(runs[True], runs[False]):
+        close(ref, got_tc, "bfloat16", "tensor-core attention", whole=got_general)
+        close(ref, got_general, "bfloat16", "general attention")
+    close(ref, run_pieces(engine(models, "wide", "float32"), toks, [150, 151, 400]), "float32", "wide in 32-bit")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
