@@ -21,22 +21,30 @@ struct PrepArgs {
     int vmix;        // 0: none, 1: write v_first, 2: mix with v_first
 };
 
-constexpr int PREP_THREADS = 128;
+constexpr int PREP_THREADS = 256;
 
-template <typename T>
-__device__ __forceinline__ float normed_rotated(const T* __restrict__ src, const VecRef& gain, int head0, int d, float r,
-                                                const float* __restrict__ cosr, const float* __restrict__ sinr, int rot) {
-    // src: the projection's row; head0: index of the head's first element in the projection (and in the gain)
-    const float x = to_f32(src[head0 + d]) * r * gain.at(head0 + d);
-    if (d >= rot) return x;
+// Norms and rotates one projection (n_heads heads of `dim`) of a row into dst, whose heads are `dimp` wide: the
+// rotated pairs (i, i + rot/2) first, a thread a pair, so that each input, gain and table entry is read once; then
+// the dimensions behind the rotated ones, and the zero padding.
+template <typename T, typename TD>
+__device__ __forceinline__ void norm_rotate_heads(const T* __restrict__ src, const VecRef& gain, float r, int n_heads,
+                                                  int dim, int dimp, int rot, const float* __restrict__ cosr,
+                                                  const float* __restrict__ sinr, TD* __restrict__ dst, size_t head_stride) {
     const int half = rot >> 1;
-    if (d < half) {
-        const float y = to_f32(src[head0 + d + half]) * r * gain.at(head0 + d + half);
-        return x * cosr[d] - y * sinr[d];
+    for (int idx = threadIdx.x; idx < n_heads * half; idx += PREP_THREADS) {
+        const int h = idx / half, i = idx % half;
+        const int at = h * dim + i;
+        const float u = to_f32(src[at]) * r * gain.at(at);
+        const float v = to_f32(src[at + half]) * r * gain.at(at + half);
+        const float c = cosr[i], sn = sinr[i];
+        dst[h * head_stride + i] = from_f32<TD>(u * c - v * sn);
+        dst[h * head_stride + i + half] = from_f32<TD>(v * c + u * sn);
     }
-    const int j = d - half;
-    const float y = to_f32(src[head0 + j]) * r * gain.at(head0 + j);
-    return x * cosr[j] + y * sinr[j];
+    const int rest = dimp - rot;
+    for (int idx = threadIdx.x; idx < n_heads * rest; idx += PREP_THREADS) {
+        const int h = idx / rest, d = rot + idx % rest;
+        dst[h * head_stride + d] = from_f32<TD>(d < dim ? to_f32(src[h * dim + d]) * r * gain.at(h * dim + d) : 0.f);
+    }
 }
 
 template <typename T>
@@ -72,10 +80,7 @@ attn_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, VecRef qw, Ve
         sq = fmaf(v, v, sq);
     }
     const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)nq + a.eps);
-    for (int i = threadIdx.x; i < a.H * a.dimp; i += PREP_THREADS) {
-        const int h = i / a.dimp, d = i % a.dimp;
-        qo[i] = from_f32<T>(d < a.dim ? normed_rotated(src, qw, h * a.dim, d, rq, cosr, sinr, a.rot) : 0.f);
-    }
+    norm_rotate_heads(src, qw, rq, a.H, a.dim, a.dimp, a.rot, cosr, sinr, qo, (size_t)a.dimp);
     if (k_cache == nullptr) return;                // this run reads a cache that another run wrote
 
     const int page = page_of(pt, b, pos);
@@ -91,11 +96,8 @@ attn_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, VecRef qw, Ve
     }
     const float rk = 1.0f / sqrtf(block_sum(sk, red) / (float)nk + a.eps);
     const int in_page = pos % PAGE_TOKENS;
-    for (int i = threadIdx.x; i < a.G * a.dimp; i += PREP_THREADS) {
-        const int g = i / a.dimp, d = i % a.dimp;
-        const float v = d < a.dim ? normed_rotated(ksrc, kw, g * a.dim, d, rk, cosr, sinr, a.rot) : 0.f;
-        k_cache[(((size_t)page * a.G + g) * PAGE_TOKENS + in_page) * a.dimp + d] = from_f32<T>(v);
-    }
+    norm_rotate_heads(ksrc, kw, rk, a.G, a.dim, a.dimp, a.rot, cosr, sinr,
+                      k_cache + ((size_t)page * a.G * PAGE_TOKENS + in_page) * a.dimp, (size_t)PAGE_TOKENS * a.dimp);
 
     // values: a warp a head
     const T* vsrc = ksrc + nk;

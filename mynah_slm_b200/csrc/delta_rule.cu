@@ -10,9 +10,10 @@
 //   delta_rule    the recurrence. The columns of S are independent given k, q, g and beta, so a CTA takes a
 //                 tile of columns of one head of one sequence; a column's dim values are spread over L adjacent
 //                 lanes (about 16 values a lane, in registers) that add their parts of the two dot products
-//                 by shuffles in a fixed order. Sixteen tokens' keys, queries, values, decays and betas are
-//                 staged in shared memory at a time, so that the chain from token to token waits on no load
-//                 from global memory. S is fp32 [n_slots + 1][H][dim][vd], carried per slot.
+//                 by shuffles in a fixed order. Half of the CTA's threads compute; the other half stage the next
+//                 sixteen tokens' keys, queries, values, decays and betas in shared memory (two buffers) and
+//                 write the last sixteen outputs, so that the chain from token to token waits on no load from
+//                 global memory. S is fp32 [n_slots + 1][H][dim][vd], carried per slot.
 //   gated_rmsnorm out = o / rms(o over the head's vd) * w[d] * silu(gate)
 //
 // All arithmetic is fp32. A sequence's rows are walked in order, so a prompt run whole, in pieces or token by
@@ -65,6 +66,7 @@ struct DeltaArgs {
     int B, H, G, dim, vd, n_slots, ldv;
     int L;                                   // lanes a column (a power of two)
     int per;                                 // key values a lane: ceil(dim / L) rounded up to a multiple of 4
+    int vec;                                 // 1: keys and queries can be fetched four values at a time
 };
 
 // Keys and queries of a staged token lie in shared memory lane chunk by lane chunk: `per` values, then zeros up to
@@ -73,7 +75,7 @@ struct DeltaArgs {
 __device__ __forceinline__ int kq_slot(int i, int per, int stride) { return (i / per) * stride + i % per; }
 
 template <typename T, int RMAX>
-__global__ void __launch_bounds__(DELTA_THREADS)
+__global__ void __launch_bounds__(2 * DELTA_THREADS)
 delta_rule_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const T* __restrict__ v,
                   const float* __restrict__ g, const float* __restrict__ beta, float* __restrict__ state,
                   float* __restrict__ o, const int* __restrict__ cu_q, const int* __restrict__ slots, DeltaArgs a) {
@@ -85,87 +87,135 @@ delta_rule_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
     if (slot < 0 || slot >= a.n_slots || q1 <= q0) return;
     const int L = a.L, per = a.per;
     const int JT = DELTA_THREADS / L;                            // columns of this CTA
-    const int l = threadIdx.x % L, jl = threadIdx.x / L;
+    const bool stager = threadIdx.x >= DELTA_THREADS;            // the second half of the CTA stages, the first computes
+    const int tid = threadIdx.x % DELTA_THREADS;
+    const int l = tid % L, jl = tid / L;
     const int j = blockIdx.x * JT + jl;
     const bool on = j < a.vd;
     const int jj = on ? j : a.vd - 1;
     const int kvh = h / (a.H / a.G);
     constexpr int CS = RMAX + 4;                                 // floats of a lane's chunk
     const int row = CS * L;                                      // floats of a staged key (or query)
-    float* ks = sm;                                              // [TB][row]
-    float* qs = ks + DELTA_TB * row;                             // [TB][row]
-    float* vs = qs + DELTA_TB * row;                             // [TB][JT]
-    float* os = vs + DELTA_TB * JT;                              // [TB][JT]
-    float* gs = os + DELTA_TB * JT;                              // [TB] decay, [TB] beta
-    for (int i = threadIdx.x; i < 2 * DELTA_TB * row; i += DELTA_THREADS) ks[i] = 0.f;      // the unused slots stay zero
+    const int nk = DELTA_TB * row, nv = DELTA_TB * JT;
+    float* ks = sm;                                              // [2][TB][row]
+    float* qs = ks + 2 * nk;                                     // [2][TB][row]
+    float* vs = qs + 2 * nk;                                     // [2][TB][JT]
+    float* os = vs + 2 * nv;                                     // [2][TB][JT]
+    float* gs = os + 2 * nv;                                     // [2][2][TB]: decay, beta
+    for (int i = threadIdx.x; i < 4 * nk; i += 2 * DELTA_THREADS) ks[i] = 0.f;      // the unused slots stay zero
+    __syncthreads();
+
+    auto stage = [&](int k) {                                    // block k of the sequence's rows -> buffer k & 1
+        const int t0 = q0 + k * DELTA_TB, nt = min(DELTA_TB, q1 - t0), buf = k & 1;
+        if (a.vec) {
+            // four consecutive values a load, four loads of k and of q a thread issued before the first is used
+            const int d4 = a.dim / 4, total = nt * d4;
+            for (int base = tid; base < total; base += 4 * DELTA_THREADS) {
+                float4 kk[4], qq[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int idx = base + e * DELTA_THREADS;
+                    if (idx < total) {
+                        const size_t src = ((size_t)(t0 + idx / d4) * a.G + kvh) * a.dim + (size_t)(idx % d4) * 4;
+                        kk[e] = *reinterpret_cast<const float4*>(kn + src);
+                        qq[e] = *reinterpret_cast<const float4*>(qn + src);
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int idx = base + e * DELTA_THREADS;
+                    if (idx < total) {
+                        const int at = buf * nk + (idx / d4) * row + kq_slot((idx % d4) * 4, per, CS);
+                        *reinterpret_cast<float4*>(ks + at) = kk[e];
+                        *reinterpret_cast<float4*>(qs + at) = qq[e];
+                    }
+                }
+            }
+        }
+#pragma unroll 4
+        for (int idx = tid; idx < (a.vec ? 0 : nt * a.dim); idx += DELTA_THREADS) {
+            const int tt = idx / a.dim, i = idx % a.dim;
+            const size_t src = ((size_t)(t0 + tt) * a.G + kvh) * a.dim + i;
+            const int at = buf * nk + tt * row + kq_slot(i, per, CS);
+            ks[at] = kn[src];
+            qs[at] = qn[src];
+        }
+        for (int idx = tid; idx < nt * JT; idx += DELTA_THREADS) {
+            const int tt = idx / JT, col = blockIdx.x * JT + idx % JT;
+            vs[buf * nv + idx] = col < a.vd ? to_f32(v[(size_t)(t0 + tt) * a.ldv + (size_t)h * a.vd + col]) : 0.f;
+        }
+        if (tid < nt) {
+            gs[buf * 2 * DELTA_TB + tid] = g[(size_t)(t0 + tid) * a.H + h];
+            gs[buf * 2 * DELTA_TB + DELTA_TB + tid] = beta[(size_t)(t0 + tid) * a.H + h];
+        }
+    };
+    auto write_out = [&](int k) {
+        const int t0 = q0 + k * DELTA_TB, nt = min(DELTA_TB, q1 - t0), buf = k & 1;
+        for (int idx = tid; idx < nt * JT; idx += DELTA_THREADS) {
+            const int tt = idx / JT, col = blockIdx.x * JT + idx % JT;
+            if (col < a.vd) o[(size_t)(t0 + tt) * a.H * a.vd + (size_t)h * a.vd + col] = os[buf * nv + idx];
+        }
+    };
 
     float S[RMAX];
     float* st = state + (((size_t)slot * a.H + h) * a.dim) * a.vd + jj;
     const int i0 = l * per;
+    if (!stager) {
 #pragma unroll
-    for (int r = 0; r < RMAX; r++) S[r] = (r < per && i0 + r < a.dim) ? st[(size_t)(i0 + r) * a.vd] : 0.f;
-
-    for (int t0 = q0; t0 < q1; t0 += DELTA_TB) {
-        const int nt = min(DELTA_TB, q1 - t0);
-        __syncthreads();                                         // the block before is consumed (and the zeroing done)
-        for (int idx = threadIdx.x; idx < nt * a.dim; idx += DELTA_THREADS) {
-            const int tt = idx / a.dim, i = idx % a.dim;
-            const size_t src = ((size_t)(t0 + tt) * a.G + kvh) * a.dim + i;
-            ks[tt * row + kq_slot(i, per, CS)] = kn[src];
-            qs[tt * row + kq_slot(i, per, CS)] = qn[src];
-        }
-        for (int idx = threadIdx.x; idx < nt * JT; idx += DELTA_THREADS) {
-            const int tt = idx / JT, c = idx % JT;
-            const int col = blockIdx.x * JT + c;
-            vs[idx] = col < a.vd ? to_f32(v[(size_t)(t0 + tt) * a.ldv + (size_t)h * a.vd + col]) : 0.f;
-        }
-        if (threadIdx.x < nt) {
-            gs[threadIdx.x] = g[(size_t)(t0 + threadIdx.x) * a.H + h];
-            gs[DELTA_TB + threadIdx.x] = beta[(size_t)(t0 + threadIdx.x) * a.H + h];
-        }
-        __syncthreads();
-        for (int tt = 0; tt < nt; tt++) {
-            const float gt = gs[tt], bt = gs[DELTA_TB + tt];
-            const float4* k4 = reinterpret_cast<const float4*>(ks + tt * row + l * CS);
-            const float4* q4 = reinterpret_cast<const float4*>(qs + tt * row + l * CS);
-            float kr[RMAX];
-            float dot = 0.f;
-#pragma unroll
-            for (int r = 0; r < RMAX; r += 4) {
-                const float4 kk = k4[r >> 2];
-                kr[r] = kk.x; kr[r + 1] = kk.y; kr[r + 2] = kk.z; kr[r + 3] = kk.w;
-            }
-#pragma unroll
-            for (int r = 0; r < RMAX; r++) {
-                S[r] *= gt;
-                dot = fmaf(S[r], kr[r], dot);
-            }
-            for (int s = L >> 1; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
-            const float u = bt * (vs[tt * JT + jl] - dot);
-            float out = 0.f;
-#pragma unroll
-            for (int r = 0; r < RMAX; r += 4) {
-                const float4 qq = q4[r >> 2];
-                S[r] = fmaf(kr[r], u, S[r]);
-                S[r + 1] = fmaf(kr[r + 1], u, S[r + 1]);
-                S[r + 2] = fmaf(kr[r + 2], u, S[r + 2]);
-                S[r + 3] = fmaf(kr[r + 3], u, S[r + 3]);
-                out = fmaf(S[r], qq.x, out);
-                out = fmaf(S[r + 1], qq.y, out);
-                out = fmaf(S[r + 2], qq.z, out);
-                out = fmaf(S[r + 3], qq.w, out);
-            }
-            for (int s = L >> 1; s > 0; s >>= 1) out += __shfl_xor_sync(0xffffffffu, out, s);
-            if (l == 0) os[tt * JT + jl] = out;
-        }
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * JT; idx += DELTA_THREADS) {
-            const int tt = idx / JT, c = idx % JT;
-            const int col = blockIdx.x * JT + c;
-            if (col < a.vd) o[(size_t)(t0 + tt) * a.H * a.vd + (size_t)h * a.vd + col] = os[idx];
-        }
+        for (int r = 0; r < RMAX; r++) S[r] = (r < per && i0 + r < a.dim) ? st[(size_t)(i0 + r) * a.vd] : 0.f;
+    } else {
+        stage(0);
     }
-    if (on) {
+    __syncthreads();
+    const int n_blocks = (q1 - q0 + DELTA_TB - 1) / DELTA_TB;
+    for (int k = 0; k < n_blocks; k++) {
+        if (stager) {
+            if (k + 1 < n_blocks) stage(k + 1);
+            if (k > 0) write_out(k - 1);
+        } else {
+            const int nt = min(DELTA_TB, q1 - q0 - k * DELTA_TB), buf = k & 1;
+            for (int tt = 0; tt < nt; tt++) {
+                const float gt = gs[buf * 2 * DELTA_TB + tt], bt = gs[buf * 2 * DELTA_TB + DELTA_TB + tt];
+                const float4* k4 = reinterpret_cast<const float4*>(ks + buf * nk + tt * row + l * CS);
+                const float4* q4 = reinterpret_cast<const float4*>(qs + buf * nk + tt * row + l * CS);
+                float kr[RMAX];
+                float d4[4] = {0.f, 0.f, 0.f, 0.f};             // four partial sums: four short chains instead of a long one
+#pragma unroll
+                for (int r = 0; r < RMAX; r += 4) {
+                    const float4 kk = k4[r >> 2];
+                    kr[r] = kk.x; kr[r + 1] = kk.y; kr[r + 2] = kk.z; kr[r + 3] = kk.w;
+                }
+#pragma unroll
+                for (int r = 0; r < RMAX; r++) {
+                    S[r] *= gt;
+                    d4[r & 3] = fmaf(S[r], kr[r], d4[r & 3]);
+                }
+                float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+                for (int s = L >> 1; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
+                const float u = bt * (vs[buf * nv + tt * JT + jl] - dot);
+                float o4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int r = 0; r < RMAX; r += 4) {
+                    const float4 qq = q4[r >> 2];
+                    S[r] = fmaf(kr[r], u, S[r]);
+                    S[r + 1] = fmaf(kr[r + 1], u, S[r + 1]);
+                    S[r + 2] = fmaf(kr[r + 2], u, S[r + 2]);
+                    S[r + 3] = fmaf(kr[r + 3], u, S[r + 3]);
+                    o4[0] = fmaf(S[r], qq.x, o4[0]);
+                    o4[1] = fmaf(S[r + 1], qq.y, o4[1]);
+                    o4[2] = fmaf(S[r + 2], qq.z, o4[2]);
+                    o4[3] = fmaf(S[r + 3], qq.w, o4[3]);
+                }
+                float out = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+                for (int s = L >> 1; s > 0; s >>= 1) out += __shfl_xor_sync(0xffffffffu, out, s);
+                if (l == 0) os[buf * nv + tt * JT + jl] = out;
+            }
+        }
+        __syncthreads();
+    }
+    if (stager) {
+        write_out(n_blocks - 1);
+    } else if (on) {
 #pragma unroll
         for (int r = 0; r < RMAX; r++)
             if (r < per && i0 + r < a.dim) st[(size_t)(i0 + r) * a.vd] = S[r];
@@ -231,16 +281,17 @@ MYNAH_API int mynah_delta_rule(const float* qn, const float* kn, const void* v, 
     int L = 1;
     while (L * 16 < dim && L < 32) L <<= 1;                     // about 16 key values a lane
     const int per = (ceil_div(dim, L) + 3) / 4 * 4;
-    const DeltaArgs a{B, H, G, dim, vd, n_slots, ldv, L, per};
+    const int vec = dim % 4 == 0 && ((reinterpret_cast<uintptr_t>(qn) | reinterpret_cast<uintptr_t>(kn)) & 15) == 0;
+    const DeltaArgs a{B, H, G, dim, vd, n_slots, ldv, L, per, vec};
     const int JT = DELTA_THREADS / L;
     const dim3 grid(ceil_div(vd, JT), H, B);
     const int rmax = per <= 16 ? 16 : 32;
-    const size_t smem = sizeof(float) * ((size_t)2 * DELTA_TB * (rmax + 4) * L + (size_t)2 * DELTA_TB * JT + 2 * DELTA_TB);
+    const size_t smem = sizeof(float) * ((size_t)4 * DELTA_TB * (rmax + 4) * L + (size_t)4 * DELTA_TB * JT + 4 * DELTA_TB);
 #define DELTA_LAUNCH(T, RMAX)                                                                                          \
     if (smem > 48 * 1024 &&                                                                                            \
         cudaFuncSetAttribute(delta_rule_kernel<T, RMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
         return mynah_fail("delta_rule: %zu bytes of shared memory are not to be had", smem);                          \
-    mynah_launch(delta_rule_kernel<T, RMAX>, grid, dim3(DELTA_THREADS), smem, stream, qn, kn, (const T*)v, g, beta, state, o, \
+    mynah_launch(delta_rule_kernel<T, RMAX>, grid, dim3(2 * DELTA_THREADS), smem, stream, qn, kn, (const T*)v, g, beta, state, o, \
                  cu_q, slots, a)
     if (dtype != MYNAH_F32 && dtype != MYNAH_BF16) return mynah_fail("delta_rule: unsupported dtype %d", dtype);
     if (rmax == 16) {

@@ -325,9 +325,33 @@ __global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out,
     if (i < n) out[i] = from_f32<T>(act_apply(to_f32(in[i]), act));
 }
 
+// eight consecutive elements a thread, 16-byte vectors
+template <typename T>
+__global__ void activation8_kernel(const T* __restrict__ in, T* __restrict__ out, long long n8, int act) {
+    griddep_launch_small();
+    griddep_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    float v[8];
+    load8(in + i * 8, v);
+#pragma unroll
+    for (int k = 0; k < 8; k++) v[k] = act_apply(v[k], act);
+    store8(out + i * 8, v);
+}
+
 MYNAH_API int mynah_activation(const void* in, void* out, int dtype, long long n, int act, cudaStream_t stream) {
     if (n == 0) return 0;
     MYNAH_REQUIRE(n > 0 && act >= 0 && act <= 3, "activation: bad arguments n=%lld act=%d", n, act);
+    if (n % 8 == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 31) == 0 &&
+        (dtype == MYNAH_F32 || dtype == MYNAH_BF16)) {
+        const long long n8 = n / 8;
+        const unsigned blocks8 = (unsigned)ceil_div_ll(n8, 256);
+        if (dtype == MYNAH_F32)
+            mynah_launch(activation8_kernel<float>, dim3(blocks8), dim3(256), 0, stream, (const float*)in, (float*)out, n8, act);
+        else
+            mynah_launch(activation8_kernel<bf16>, dim3(blocks8), dim3(256), 0, stream, (const bf16*)in, (bf16*)out, n8, act);
+        return mynah_check_launch("activation");
+    }
     const unsigned blocks = (unsigned)ceil_div_ll(n, 256);
     if (dtype == MYNAH_F32)
         mynah_launch(activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)in, (float*)out, n, act);

@@ -17,25 +17,26 @@
 
 namespace {
 
-constexpr int SCAN_THREADS = 128;
+constexpr int SCAN_THREADS = 128;              // threads that compute; as many again stage the inputs
 constexpr int SCAN_R = 8;                     // state values a lane
-constexpr int SCAN_TB = 32;                   // tokens staged in shared memory at a time
+constexpr int SCAN_TB = 16;                   // tokens staged in shared memory at a time
 
 struct ScanArgs {
     int B, inner, N, n_slots;
     int ldx, lddt, ldbc, ldz, ldy;
     int NL;                                   // lanes a channel
+    int vec;                                  // 1: rows, strides and addresses fit 16-byte (fp32: 32-byte) vectors
 };
 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
-// Thirty-two tokens at a time are staged in shared memory: the CTA's channels of x and of the step size (softplus
-// applied on the way in), and the tokens' B and C, each lane's SCAN_R values followed by 4 unused floats so that the
-// lanes of a channel read 16-byte vectors from different banks. The chain from token to token then waits on no
-// load from global memory; y = (S.C + D x) silu(z) goes back through shared memory, so that z is read and y written
-// in whole rows.
+// A CTA has 128 computing threads and 128 staging threads. Sixteen tokens at a time go through shared memory, in two
+// buffers: while the computing threads walk block k, the staging threads bring block k+1 (the CTA's channels of x, of
+// the step size with its softplus applied, of silu(z), and the tokens' B and C, each lane's SCAN_R values followed by
+// 4 unused floats so that the lanes of a channel read 16-byte vectors from different banks) and write block k-1's
+// y = (S.C + D x) silu(z) out in whole rows. The chain from token to token then waits on no load from global memory.
 template <typename TX, typename TD>
-__global__ void __launch_bounds__(SCAN_THREADS)
+__global__ void __launch_bounds__(2 * SCAN_THREADS)
 selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt_raw, VecRef dt_bias, VecRef A_log, VecRef Dv,
                       const TD* __restrict__ Bm, const TD* __restrict__ Cm, const TX* __restrict__ z,
                       float* __restrict__ state, TX* __restrict__ y,
@@ -48,77 +49,136 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt_raw
     if (slot < 0 || slot >= a.n_slots || q1 <= q0) return;
     const int NL = a.NL;
     const int CB = SCAN_THREADS / NL;             // channels of this CTA
-    const int l = threadIdx.x % NL, cl = threadIdx.x / NL;
+    const bool stager = threadIdx.x >= SCAN_THREADS;
+    const int tid = threadIdx.x % SCAN_THREADS;
+    const int l = tid % NL, cl = tid / NL;
     const int c0 = blockIdx.x * CB;
     const int c = c0 + cl;
     const bool on = c < a.inner;
     const int cc = on ? c : a.inner - 1;          // lanes past the last channel compute and store nothing
     constexpr int CS = SCAN_R + 4;
     const int brow = CS * NL;
-    float* xs = sm;                               // [TB][CB]
-    float* ds = xs + SCAN_TB * CB;                // [TB][CB] step sizes
-    float* ys = ds + SCAN_TB * CB;                // [TB][CB]
-    float* bs = ys + SCAN_TB * CB;                // [TB][brow]
-    float* cs = bs + SCAN_TB * brow;              // [TB][brow]
-    for (int i = threadIdx.x; i < 2 * SCAN_TB * brow; i += SCAN_THREADS) bs[i] = 0.f;
+    const int nx = SCAN_TB * CB, nb = SCAN_TB * brow;
+    float* xs = sm;                               // [2][TB][CB]
+    float* ds = xs + 2 * nx;                      // [2][TB][CB] step sizes
+    float* zs = ds + 2 * nx;                      // [2][TB][CB] silu(z)
+    float* ys = zs + 2 * nx;                      // [2][TB][CB]
+    float* bs = ys + 2 * nx;                      // [2][TB][brow]
+    float* cs = bs + 2 * nb;                      // [2][TB][brow]
+    for (int i = threadIdx.x; i < 4 * nb; i += 2 * SCAN_THREADS) bs[i] = 0.f;     // the unused slots stay zero
+    __syncthreads();
 
-    float S[SCAN_R], A[SCAN_R];
-    float* st = state + ((size_t)slot * a.inner + cc) * a.N;
+    auto stage = [&](int k) {                     // block k of the sequence's rows -> buffer k & 1
+        const int t0 = q0 + k * SCAN_TB, nt = min(SCAN_TB, q1 - t0), buf = k & 1;
+        if (a.vec) {
+            // eight consecutive channels a thread (at most one such piece of x, z and the step a thread, since a CTA
+            // has at most 64 channels), every load issued before the first is used
+            const int per_row = CB / 8;
+            const int tt = tid / per_row, c8 = (tid % per_row) * 8;
+            const bool act = tid < nt * per_row && c0 + c8 < a.inner;
+            float xv[8], zv[8], dv[8];
+            if (act) {
+                load8(x + (size_t)(t0 + tt) * a.ldx + c0 + c8, xv);
+                load8(z + (size_t)(t0 + tt) * a.ldz + c0 + c8, zv);
+                load8(dt_raw + (size_t)(t0 + tt) * a.lddt + c0 + c8, dv);
+            }
+            const int n8 = a.N / 8;
+            for (int idx = tid; idx < nt * n8; idx += SCAN_THREADS) {
+                const int bt = idx / n8, g8 = idx % n8;
+                float bv[8], cv[8];
+                load8(Bm + (size_t)(t0 + bt) * a.ldbc + g8 * 8, bv);
+                load8(Cm + (size_t)(t0 + bt) * a.ldbc + g8 * 8, cv);
+                store8(bs + buf * nb + bt * brow + g8 * CS, bv);
+                store8(cs + buf * nb + bt * brow + g8 * CS, cv);
+            }
+            if (tid < nt * per_row) {
 #pragma unroll
-    for (int r = 0; r < SCAN_R; r++) {
-        const int n = l * SCAN_R + r;
-        S[r] = n < a.N ? st[n] : 0.f;
-        A[r] = n < a.N ? -expf(A_log.at(cc * a.N + n)) : 0.f;
-    }
-    const float Dc = Dv.p ? Dv.at(cc) : 0.f;
-
-    for (int t0 = q0; t0 < q1; t0 += SCAN_TB) {
-        const int nt = min(SCAN_TB, q1 - t0);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * CB; idx += SCAN_THREADS) {
+                for (int e = 0; e < 8; e++) {
+                    xv[e] = act ? xv[e] : 0.f;
+                    dv[e] = act ? softplus_f(dv[e] + (dt_bias.p ? dt_bias.at(c0 + c8 + e) : 0.f)) : 0.f;
+                    zv[e] = act ? zv[e] / (1.0f + expf(-zv[e])) : 0.f;
+                }
+                store8(xs + buf * nx + tt * CB + c8, xv);
+                store8(ds + buf * nx + tt * CB + c8, dv);
+                store8(zs + buf * nx + tt * CB + c8, zv);
+            }
+            return;
+        }
+#pragma unroll 4
+        for (int idx = tid; idx < nt * CB; idx += SCAN_THREADS) {
             const int tt = idx / CB, ch = c0 + idx % CB;
             const bool ok = ch < a.inner;
-            xs[idx] = ok ? to_f32(x[(size_t)(t0 + tt) * a.ldx + ch]) : 0.f;
-            ds[idx] = ok ? softplus_f(dt_raw[(size_t)(t0 + tt) * a.lddt + ch] + (dt_bias.p ? dt_bias.at(ch) : 0.f)) : 0.f;
+            const float zv = ok ? to_f32(z[(size_t)(t0 + tt) * a.ldz + ch]) : 0.f;
+            xs[buf * nx + idx] = ok ? to_f32(x[(size_t)(t0 + tt) * a.ldx + ch]) : 0.f;
+            ds[buf * nx + idx] = ok ? softplus_f(dt_raw[(size_t)(t0 + tt) * a.lddt + ch] + (dt_bias.p ? dt_bias.at(ch) : 0.f)) : 0.f;
+            zs[buf * nx + idx] = zv / (1.0f + expf(-zv));
         }
-        for (int idx = threadIdx.x; idx < nt * a.N; idx += SCAN_THREADS) {
+#pragma unroll 4
+        for (int idx = tid; idx < nt * a.N; idx += SCAN_THREADS) {
             const int tt = idx / a.N, n = idx % a.N;
-            const int at = tt * brow + (n / SCAN_R) * CS + n % SCAN_R;
+            const int at = buf * nb + tt * brow + (n / SCAN_R) * CS + n % SCAN_R;
             bs[at] = to_f32(Bm[(size_t)(t0 + tt) * a.ldbc + n]);
             cs[at] = to_f32(Cm[(size_t)(t0 + tt) * a.ldbc + n]);
         }
-        __syncthreads();
-        for (int tt = 0; tt < nt; tt++) {
-            const float xv = xs[tt * CB + cl], dt = ds[tt * CB + cl];
-            const float dx = dt * xv;
-            const float4* b4 = reinterpret_cast<const float4*>(bs + tt * brow + l * CS);
-            const float4* c4 = reinterpret_cast<const float4*>(cs + tt * brow + l * CS);
-            float acc = 0.f;
-#pragma unroll
-            for (int r = 0; r < SCAN_R; r += 4) {
-                const float4 bb = b4[r >> 2], cv = c4[r >> 2];
-                S[r] = fmaf(expf(dt * A[r]), S[r], dx * bb.x);
-                S[r + 1] = fmaf(expf(dt * A[r + 1]), S[r + 1], dx * bb.y);
-                S[r + 2] = fmaf(expf(dt * A[r + 2]), S[r + 2], dx * bb.z);
-                S[r + 3] = fmaf(expf(dt * A[r + 3]), S[r + 3], dx * bb.w);
-                acc = fmaf(S[r], cv.x, acc);
-                acc = fmaf(S[r + 1], cv.y, acc);
-                acc = fmaf(S[r + 2], cv.z, acc);
-                acc = fmaf(S[r + 3], cv.w, acc);
-            }
-            for (int o = NL >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (l == 0) ys[tt * CB + cl] = acc + Dc * xv;
-        }
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * CB; idx += SCAN_THREADS) {
+    };
+    auto write_out = [&](int k) {                 // y of block k, from buffer k & 1
+        const int t0 = q0 + k * SCAN_TB, nt = min(SCAN_TB, q1 - t0), buf = k & 1;
+        for (int idx = tid; idx < nt * CB; idx += SCAN_THREADS) {
             const int tt = idx / CB, ch = c0 + idx % CB;
-            if (ch < a.inner) {
-                const float zv = to_f32(z[(size_t)(t0 + tt) * a.ldz + ch]);
-                y[(size_t)(t0 + tt) * a.ldy + ch] = from_f32<TX>(ys[idx] * (zv / (1.0f + expf(-zv))));
+            if (ch < a.inner) y[(size_t)(t0 + tt) * a.ldy + ch] = from_f32<TX>(ys[buf * nx + idx]);
+        }
+    };
+
+    float S[SCAN_R], A[SCAN_R];
+    float* st = state + ((size_t)slot * a.inner + cc) * a.N;
+    float Dc = 0.f;
+    if (!stager) {
+#pragma unroll
+        for (int r = 0; r < SCAN_R; r++) {
+            const int n = l * SCAN_R + r;
+            S[r] = n < a.N ? st[n] : 0.f;
+            A[r] = n < a.N ? -expf(A_log.at(cc * a.N + n)) : 0.f;
+        }
+        Dc = Dv.p ? Dv.at(cc) : 0.f;
+    } else {
+        stage(0);
+    }
+    __syncthreads();
+    const int n_blocks = (q1 - q0 + SCAN_TB - 1) / SCAN_TB;
+    for (int k = 0; k < n_blocks; k++) {
+        if (stager) {
+            if (k + 1 < n_blocks) stage(k + 1);
+            if (k > 0) write_out(k - 1);
+        } else {
+            const int nt = min(SCAN_TB, q1 - q0 - k * SCAN_TB), buf = k & 1;
+            for (int tt = 0; tt < nt; tt++) {
+                const float xv = xs[buf * nx + tt * CB + cl], dt = ds[buf * nx + tt * CB + cl];
+                const float dx = dt * xv;
+                const float4* b4 = reinterpret_cast<const float4*>(bs + buf * nb + tt * brow + l * CS);
+                const float4* c4 = reinterpret_cast<const float4*>(cs + buf * nb + tt * brow + l * CS);
+                float a4[4] = {0.f, 0.f, 0.f, 0.f};             // four partial sums: short chains
+#pragma unroll
+                for (int r = 0; r < SCAN_R; r += 4) {
+                    const float4 bb = b4[r >> 2], cv = c4[r >> 2];
+                    S[r] = fmaf(expf(dt * A[r]), S[r], dx * bb.x);
+                    S[r + 1] = fmaf(expf(dt * A[r + 1]), S[r + 1], dx * bb.y);
+                    S[r + 2] = fmaf(expf(dt * A[r + 2]), S[r + 2], dx * bb.z);
+                    S[r + 3] = fmaf(expf(dt * A[r + 3]), S[r + 3], dx * bb.w);
+                    a4[0] = fmaf(S[r], cv.x, a4[0]);
+                    a4[1] = fmaf(S[r + 1], cv.y, a4[1]);
+                    a4[2] = fmaf(S[r + 2], cv.z, a4[2]);
+                    a4[3] = fmaf(S[r + 3], cv.w, a4[3]);
+                }
+                float acc = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+                for (int o = NL >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (l == 0) ys[buf * nx + tt * CB + cl] = (acc + Dc * xv) * zs[buf * nx + tt * CB + cl];
             }
         }
+        __syncthreads();
     }
-    if (on) {
+    if (stager) {
+        write_out(n_blocks - 1);
+    } else if (on) {
 #pragma unroll
         for (int r = 0; r < SCAN_R; r++) {
             const int n = l * SCAN_R + r;
@@ -141,17 +201,20 @@ MYNAH_API int mynah_selective_scan(const void* x, int ldx, const void* z, int ld
     MYNAH_REQUIRE(B > 0 && inner > 0 && N > 0, "selective_scan: bad sizes B=%d inner=%d N=%d", B, inner, N);
     MYNAH_REQUIRE(N <= 32 * SCAN_R, "selective_scan: a state of %d values a channel exceeds %d", N, 32 * SCAN_R);
     MYNAH_REQUIRE(B <= 65535, "selective_scan: %d sequences exceed one launch", B);
-    int NL = 1;
+    int NL = 2;                                                 // at least two: a CTA then stages at most 64 channels
     while (NL * SCAN_R < N) NL <<= 1;
-    const ScanArgs a{B, inner, N, n_slots, ldx, lddt, ldbc, ldz, ldy, NL};
+    auto fits = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31) == 0; };
+    const int vec = inner % 8 == 0 && N % 8 == 0 && ldx % 8 == 0 && ldz % 8 == 0 && lddt % 8 == 0 && ldbc % 8 == 0 &&
+                    (SCAN_THREADS / NL) % 8 == 0 && fits(x) && fits(z) && fits(dt_raw) && fits(Bm) && fits(Cm);
+    const ScanArgs a{B, inner, N, n_slots, ldx, lddt, ldbc, ldz, ldy, NL, vec};
     const VecRef bias{dt_bias, w_dtype}, al{A_log, w_dtype}, dv{Dv, w_dtype};
     const dim3 grid(ceil_div(inner, SCAN_THREADS / NL), B);
-    const size_t smem = sizeof(float) * ((size_t)3 * SCAN_TB * (SCAN_THREADS / NL) + (size_t)2 * SCAN_TB * (SCAN_R + 4) * NL);
+    const size_t smem = sizeof(float) * ((size_t)8 * SCAN_TB * (SCAN_THREADS / NL) + (size_t)4 * SCAN_TB * (SCAN_R + 4) * NL);
 #define SCAN_LAUNCH(TX, TD)                                                                                              \
     if (smem > 48 * 1024 &&                                                                                              \
         cudaFuncSetAttribute(selective_scan_kernel<TX, TD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
         return mynah_fail("selective_scan: %zu bytes of shared memory are not to be had", smem);                        \
-    mynah_launch(selective_scan_kernel<TX, TD>, grid, dim3(SCAN_THREADS), smem, stream, (const TX*)x, dt_raw, bias, al, \
+    mynah_launch(selective_scan_kernel<TX, TD>, grid, dim3(2 * SCAN_THREADS), smem, stream, (const TX*)x, dt_raw, bias, al, \
                  dv, (const TD*)Bm, (const TD*)Cm, (const TX*)z, state, (TX*)y, cu_q, slots, a)
     if (act_dtype == MYNAH_F32 && proj_dtype == MYNAH_F32) { SCAN_LAUNCH(float, float); }
     else if (act_dtype == MYNAH_BF16 && proj_dtype == MYNAH_F32) { SCAN_LAUNCH(bf16, float); }

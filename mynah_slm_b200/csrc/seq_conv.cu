@@ -85,11 +85,162 @@ conv_state_shift_kernel(const TI* __restrict__ x, float* __restrict__ state, con
     }
 }
 
+// The same convolution, eight consecutive channels a thread with 16-byte accesses (channels, strides and
+// addresses must fit them); the products are summed in the same order.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(128)
+causal_conv8_kernel(const TI* __restrict__ x, VecRef w, VecRef bias, float* __restrict__ state, TO* __restrict__ out,
+                    const int* __restrict__ tok_seq, const int* __restrict__ cu_q, const int* __restrict__ slots,
+                    ConvArgs a) {
+    griddep_launch_small();
+    griddep_wait();
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    const int row = blockIdx.x;
+    if (c >= a.C) return;
+    const int b = tok_seq[row];
+    TO* o = out + (size_t)row * a.ldo + c;
+    float acc[8], cur[8], v[8];
+    if (b < 0 || b >= a.B) {
+#pragma unroll
+        for (int k = 0; k < 8; k++) acc[k] = 0.f;
+        store8(o, acc);
+        return;
+    }
+    const int i = row - cu_q[b];
+    int slot = slots[b];
+    if (slot < 0 || slot >= a.n_slots) slot = a.n_slots;
+    const int hist = a.taps - 1;
+    float* st = state + (size_t)slot * hist * a.C + c;
+#pragma unroll
+    for (int k = 0; k < 8; k++) acc[k] = bias.p ? bias.at(c + k) : 0.f;
+    load8(x + (size_t)row * a.ldx + c, cur);
+    for (int j = 0; j < a.taps; j++) {
+        const int src = i - hist + j;
+        if (j == hist) {
+#pragma unroll
+            for (int k = 0; k < 8; k++) v[k] = cur[k];
+        } else if (src >= 0) {
+            load8(x + (size_t)(row - hist + j) * a.ldx + c, v);
+        } else {
+            load8(st + (size_t)(hist + src) * a.C, v);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++) acc[k] = fmaf(w.at((c + k) * a.taps + j), v[k], acc[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        if (a.act == 1) acc[k] = silu_f(acc[k]);
+        if (a.add_input) acc[k] += cur[k];
+    }
+    store8(o, acc);
+    if (a.update) {
+        for (int k = 0; k + 1 < hist; k++) {
+            load8(st + (size_t)(k + 1) * a.C, v);
+            store8(st + (size_t)k * a.C, v);
+        }
+        if (hist > 0) store8(st + (size_t)(hist - 1) * a.C, cur);
+    }
+}
+
+// Prompt steps: a thread takes eight channels of CONV_ROWS consecutive rows, keeps its 8 x taps weights and the last
+// taps-1 inputs in registers and lets the rows slide through: every input is fetched once and every weight once a
+// tile. A sequence that starts inside the tile (or the tile's first row) refills the window from the rows before it
+// or from the state. Filters of up to 4 taps; the products are summed in the same order as in the other forms.
+constexpr int CONV_ROWS = 8;
+constexpr int CONV_MAXT = 4;
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(128)
+causal_conv8_rows_kernel(const TI* __restrict__ x, VecRef w, VecRef bias, const float* __restrict__ state,
+                         TO* __restrict__ out, const int* __restrict__ tok_seq, const int* __restrict__ cu_q,
+                         const int* __restrict__ slots, ConvArgs a) {
+    griddep_launch_small();
+    griddep_wait();
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    if (c >= a.C) return;
+    const int hist = a.taps - 1;
+    float wr[CONV_MAXT][8], bb[8], win[CONV_MAXT - 1][8];
+#pragma unroll
+    for (int j = 0; j < CONV_MAXT; j++)
+#pragma unroll
+        for (int k = 0; k < 8; k++) wr[j][k] = j < a.taps ? w.at((c + k) * a.taps + j) : 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; k++) bb[k] = bias.p ? bias.at(c + k) : 0.f;
+    const int row0 = blockIdx.x * CONV_ROWS;
+    int last_b = -2;
+    for (int row = row0; row < min(row0 + CONV_ROWS, a.T); row++) {
+        const int b = tok_seq[row];
+        TO* o = out + (size_t)row * a.ldo + c;
+        float acc[8], cur[8];
+        if (b < 0 || b >= a.B) {
+#pragma unroll
+            for (int k = 0; k < 8; k++) acc[k] = 0.f;
+            store8(o, acc);
+            last_b = -2;
+            continue;
+        }
+        const int i = row - cu_q[b];
+        if (b != last_b) {                         // the window: win[m] is the input hist - m places back... filled oldest first
+            int slot = slots[b];
+            if (slot < 0 || slot >= a.n_slots) slot = a.n_slots;
+            const float* st = state + (size_t)slot * hist * a.C + c;
+#pragma unroll
+            for (int m = 0; m < CONV_MAXT - 1; m++) {
+                if (m < hist) {
+                    const int src = i - hist + m;
+                    if (src >= 0) load8(x + (size_t)(row - hist + m) * a.ldx + c, win[m]);
+                    else load8(st + (size_t)(hist + src) * a.C, win[m]);
+                }
+            }
+            last_b = b;
+        }
+        load8(x + (size_t)row * a.ldx + c, cur);
+#pragma unroll
+        for (int k = 0; k < 8; k++) acc[k] = bb[k];
+#pragma unroll
+        for (int j = 0; j < CONV_MAXT; j++) {
+            if (j < hist) {
+#pragma unroll
+                for (int k = 0; k < 8; k++) acc[k] = fmaf(wr[j][k], win[j][k], acc[k]);
+            } else if (j == hist) {
+#pragma unroll
+                for (int k = 0; k < 8; k++) acc[k] = fmaf(wr[j][k], cur[k], acc[k]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            if (a.act == 1) acc[k] = silu_f(acc[k]);
+            if (a.add_input) acc[k] += cur[k];
+        }
+        store8(o, acc);
+#pragma unroll
+        for (int m = 0; m < CONV_MAXT - 1; m++) {      // slide: drop the oldest, the current input becomes the newest
+            if (m + 1 < hist) {
+#pragma unroll
+                for (int k = 0; k < 8; k++) win[m][k] = win[m + 1][k];
+            } else if (m + 1 == hist) {
+#pragma unroll
+                for (int k = 0; k < 8; k++) win[m][k] = cur[k];
+            }
+        }
+    }
+}
+
 template <typename TI, typename TO>
 int launch_conv(const void* x, const VecRef& w, const VecRef& bias, float* state, void* out, const int* tok_seq,
                 const int* cu_q, const int* slots, const ConvArgs& a, cudaStream_t stream) {
     const int threads = a.C >= 256 ? 256 : (a.C >= 128 ? 128 : 64);
     const dim3 grid(a.T, ceil_div(a.C, threads));
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31) == 0; };
+    if (a.C % 8 == 0 && a.ldx % 8 == 0 && a.ldo % 8 == 0 && al(x) && al(out) && al(state)) {
+        const int t8 = a.C / 8 >= 128 ? 128 : (a.C / 8 >= 64 ? 64 : 32);
+        if (!a.update && a.taps <= CONV_MAXT && a.T >= 4 * CONV_ROWS)
+            mynah_launch(causal_conv8_rows_kernel<TI, TO>, dim3(ceil_div(a.T, CONV_ROWS), ceil_div(a.C / 8, t8)), dim3(t8), 0,
+                         stream, (const TI*)x, w, bias, (const float*)state, (TO*)out, tok_seq, cu_q, slots, a);
+        else
+        mynah_launch(causal_conv8_kernel<TI, TO>, dim3(a.T, ceil_div(a.C / 8, t8)), dim3(t8), 0, stream, (const TI*)x, w, bias,
+                     state, (TO*)out, tok_seq, cu_q, slots, a);
+    } else
     mynah_launch(causal_conv_kernel<TI, TO>, grid, dim3(threads), 0, stream, (const TI*)x, w, bias, state, (TO*)out,
                  tok_seq, cu_q, slots, a);
     if (mynah_check_launch("causal_conv")) return -1;
