@@ -146,7 +146,7 @@ causal_conv8_kernel(const TI* __restrict__ x, VecRef w, VecRef bias, float* __re
 // taps-1 inputs in registers and lets the rows slide through: every input is fetched once and every weight once a
 // tile. A sequence that starts inside the tile (or the tile's first row) refills the window from the rows before it
 // or from the state. Filters of up to 4 taps; the products are summed in the same order as in the other forms.
-constexpr int CONV_ROWS = 8;
+constexpr int CONV_ROWS = 4;
 constexpr int CONV_MAXT = 4;
 
 template <typename TI, typename TO>
@@ -168,10 +168,18 @@ causal_conv8_rows_kernel(const TI* __restrict__ x, VecRef w, VecRef bias, const 
     for (int k = 0; k < 8; k++) bb[k] = bias.p ? bias.at(c + k) : 0.f;
     const int row0 = blockIdx.x * CONV_ROWS;
     int last_b = -2;
-    for (int row = row0; row < min(row0 + CONV_ROWS, a.T); row++) {
+    float curs[CONV_ROWS][8];                      // every row's input is asked for before the first is used
+#pragma unroll
+    for (int r = 0; r < CONV_ROWS; r++)
+        if (row0 + r < a.T) load8(x + (size_t)(row0 + r) * a.ldx + c, curs[r]);
+#pragma unroll
+    for (int r = 0; r < CONV_ROWS; r++) {
+        const int row = row0 + r;
+        if (row >= a.T) break;
+        float (&cur)[8] = curs[r];
         const int b = tok_seq[row];
         TO* o = out + (size_t)row * a.ldo + c;
-        float acc[8], cur[8];
+        float acc[8];
         if (b < 0 || b >= a.B) {
 #pragma unroll
             for (int k = 0; k < 8; k++) acc[k] = 0.f;
@@ -194,7 +202,6 @@ causal_conv8_rows_kernel(const TI* __restrict__ x, VecRef w, VecRef bias, const 
             }
             last_b = b;
         }
-        load8(x + (size_t)row * a.ldx + c, cur);
 #pragma unroll
         for (int k = 0; k < 8; k++) acc[k] = bb[k];
 #pragma unroll
