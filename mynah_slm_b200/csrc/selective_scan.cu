@@ -26,6 +26,17 @@ struct ScanArgs {
     int ldx, lddt, ldbc, ldz, ldy;
     int NL;                                   // lanes a channel
     int vec;                                  // 1: rows, strides and addresses fit 16-byte (fp32: 32-byte) vectors
+    // Long prompts are cut into pieces of `piece` rows that run side by side, in two passes (mode 1, then mode 2):
+    //   mode 0  a CTA walks a whole sequence's rows from the slot's state (decode steps, short prompts)
+    //   mode 1  a CTA walks piece k (blockIdx.z) from a ZERO state and leaves its end state P_k and the sum of its
+    //           step sizes; the CTA of piece 0 also copies the slot's state aside
+    //   mode 2  a CTA forms its piece's true start state, S <- exp(A * sum_j) S + P_j over the pieces j before it
+    //           (the decays of a piece multiply to exp(A * sum of its step sizes)), walks the piece again and writes
+    //           y; the last piece stores the slot's new state
+    int mode, piece;
+    float* piece_state;                       // [pieces][inner][N] (P_k), pieces numbered cu_q[b] / piece + b + k
+    float* piece_dt;                          // [pieces][inner]
+    float* start_state;                       // [B][inner][N]: the slot's state as the step found it
 };
 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
@@ -45,8 +56,13 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt_raw
     griddep_wait();
     const int b = blockIdx.y;
     const int slot = slots[b];
-    const int q0 = cu_q[b], q1 = cu_q[b + 1];
-    if (slot < 0 || slot >= a.n_slots || q1 <= q0) return;
+    const int seq0 = cu_q[b], seq1 = cu_q[b + 1];
+    if (slot < 0 || slot >= a.n_slots || seq1 <= seq0) return;
+    const int piece_k = a.mode == 0 ? 0 : (int)blockIdx.z;
+    const int q0 = a.mode == 0 ? seq0 : seq0 + piece_k * a.piece;
+    if (q0 >= seq1) return;
+    const int q1 = a.mode == 0 ? seq1 : min(seq1, q0 + a.piece);
+    const size_t piece_id = (size_t)(seq0 / max(a.piece, 1) + b + piece_k);
     const int NL = a.NL;
     const int CB = SCAN_THREADS / NL;             // channels of this CTA
     const bool stager = threadIdx.x >= SCAN_THREADS;
@@ -79,7 +95,7 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt_raw
             float xv[8], zv[8], dv[8];
             if (act) {
                 load8(x + (size_t)(t0 + tt) * a.ldx + c0 + c8, xv);
-                load8(z + (size_t)(t0 + tt) * a.ldz + c0 + c8, zv);
+                if (a.mode != 1) load8(z + (size_t)(t0 + tt) * a.ldz + c0 + c8, zv);
                 load8(dt_raw + (size_t)(t0 + tt) * a.lddt + c0 + c8, dv);
             }
             const int n8 = a.N / 8;
@@ -96,7 +112,7 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt_raw
                 for (int e = 0; e < 8; e++) {
                     xv[e] = act ? xv[e] : 0.f;
                     dv[e] = act ? softplus_f(dv[e] + (dt_bias.p ? dt_bias.at(c0 + c8 + e) : 0.f)) : 0.f;
-                    zv[e] = act ? zv[e] / (1.0f + expf(-zv[e])) : 0.f;
+                    zv[e] = act && a.mode != 1 ? zv[e] / (1.0f + expf(-zv[e])) : 0.f;
                 }
                 store8(xs + buf * nx + tt * CB + c8, xv);
                 store8(ds + buf * nx + tt * CB + c8, dv);
@@ -108,7 +124,7 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt_raw
         for (int idx = tid; idx < nt * CB; idx += SCAN_THREADS) {
             const int tt = idx / CB, ch = c0 + idx % CB;
             const bool ok = ch < a.inner;
-            const float zv = ok ? to_f32(z[(size_t)(t0 + tt) * a.ldz + ch]) : 0.f;
+            const float zv = ok && a.mode != 1 ? to_f32(z[(size_t)(t0 + tt) * a.ldz + ch]) : 0.f;
             xs[buf * nx + idx] = ok ? to_f32(x[(size_t)(t0 + tt) * a.ldx + ch]) : 0.f;
             ds[buf * nx + idx] = ok ? softplus_f(dt_raw[(size_t)(t0 + tt) * a.lddt + ch] + (dt_bias.p ? dt_bias.at(ch) : 0.f)) : 0.f;
             zs[buf * nx + idx] = zv / (1.0f + expf(-zv));
@@ -122,6 +138,7 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt_raw
         }
     };
     auto write_out = [&](int k) {                 // y of block k, from buffer k & 1
+        if (a.mode == 1) return;
         const int t0 = q0 + k * SCAN_TB, nt = min(SCAN_TB, q1 - t0), buf = k & 1;
         for (int idx = tid; idx < nt * CB; idx += SCAN_THREADS) {
             const int tt = idx / CB, ch = c0 + idx % CB;
@@ -131,15 +148,36 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt_raw
 
     float S[SCAN_R], A[SCAN_R];
     float* st = state + ((size_t)slot * a.inner + cc) * a.N;
-    float Dc = 0.f;
+    float Dc = 0.f, dt_sum = 0.f;
     if (!stager) {
+        const float* init = a.mode == 2 ? a.start_state + ((size_t)b * a.inner + cc) * a.N : st;
 #pragma unroll
         for (int r = 0; r < SCAN_R; r++) {
             const int n = l * SCAN_R + r;
-            S[r] = n < a.N ? st[n] : 0.f;
+            S[r] = (n < a.N && a.mode != 1) ? init[n] : 0.f;
             A[r] = n < a.N ? -expf(A_log.at(cc * a.N + n)) : 0.f;
         }
         Dc = Dv.p ? Dv.at(cc) : 0.f;
+        if (a.mode == 1 && piece_k == 0 && on) {              // the state as the step found it, for the second pass
+            float* keep = a.start_state + ((size_t)b * a.inner + cc) * a.N;
+#pragma unroll
+            for (int r = 0; r < SCAN_R; r++) {
+                const int n = l * SCAN_R + r;
+                if (n < a.N) keep[n] = st[n];
+            }
+        }
+        if (a.mode == 2) {
+            for (int j = 0; j < piece_k; j++) {               // the pieces before this one, in order
+                const size_t pj = piece_id - piece_k + j;
+                const float sdt = a.piece_dt[pj * a.inner + cc];
+                const float* P = a.piece_state + (pj * a.inner + cc) * a.N;
+#pragma unroll
+                for (int r = 0; r < SCAN_R; r++) {
+                    const int n = l * SCAN_R + r;
+                    if (n < a.N) S[r] = fmaf(expf(sdt * A[r]), S[r], P[n]);
+                }
+            }
+        }
     } else {
         stage(0);
     }
@@ -154,6 +192,7 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt_raw
             for (int tt = 0; tt < nt; tt++) {
                 const float xv = xs[buf * nx + tt * CB + cl], dt = ds[buf * nx + tt * CB + cl];
                 const float dx = dt * xv;
+                dt_sum += dt;
                 const float4* b4 = reinterpret_cast<const float4*>(bs + buf * nb + tt * brow + l * CS);
                 const float4* c4 = reinterpret_cast<const float4*>(cs + buf * nb + tt * brow + l * CS);
                 float a4[4] = {0.f, 0.f, 0.f, 0.f};             // four partial sums: short chains
@@ -178,7 +217,15 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt_raw
     }
     if (stager) {
         write_out(n_blocks - 1);
-    } else if (on) {
+    } else if (on && a.mode == 1) {
+        float* P = a.piece_state + (piece_id * a.inner + cc) * a.N;
+#pragma unroll
+        for (int r = 0; r < SCAN_R; r++) {
+            const int n = l * SCAN_R + r;
+            if (n < a.N) P[n] = S[r];
+        }
+        if (l == 0) a.piece_dt[piece_id * a.inner + cc] = dt_sum;
+    } else if (on && (a.mode == 0 || q1 == seq1)) {
 #pragma unroll
         for (int r = 0; r < SCAN_R; r++) {
             const int n = l * SCAN_R + r;
@@ -196,7 +243,7 @@ MYNAH_API int mynah_selective_scan(const void* x, int ldx, const void* z, int ld
                                    const float* dt_raw, int lddt, const void* Bm, const void* Cm, int ldbc, int proj_dtype,
                                    const void* dt_bias, const void* A_log, const void* Dv, int w_dtype,
                                    float* state, int n_slots, const int* cu_q, const int* slots,
-                                   int B, int inner, int N, cudaStream_t stream) {
+                                   int B, int inner, int N, int piece, int n_pieces, int max_q_len, float* scratch, cudaStream_t stream) {
     if (B == 0) return 0;
     MYNAH_REQUIRE(B > 0 && inner > 0 && N > 0, "selective_scan: bad sizes B=%d inner=%d N=%d", B, inner, N);
     MYNAH_REQUIRE(N <= 32 * SCAN_R, "selective_scan: a state of %d values a channel exceeds %d", N, 32 * SCAN_R);
@@ -206,20 +253,34 @@ MYNAH_API int mynah_selective_scan(const void* x, int ldx, const void* z, int ld
     auto fits = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31) == 0; };
     const int vec = inner % 8 == 0 && N % 8 == 0 && ldx % 8 == 0 && ldz % 8 == 0 && lddt % 8 == 0 && ldbc % 8 == 0 &&
                     (SCAN_THREADS / NL) % 8 == 0 && fits(x) && fits(z) && fits(dt_raw) && fits(Bm) && fits(Cm);
-    const ScanArgs a{B, inner, N, n_slots, ldx, lddt, ldbc, ldz, ldy, NL, vec};
+    // piece > 0: the two passes over pieces of `piece` rows; scratch then holds n_pieces * inner * (N + 1) +
+    // B * inner * N floats and n_pieces >= rows / piece + B + 1
+    MYNAH_REQUIRE(piece == 0 || (piece > 0 && n_pieces > 0 && scratch != nullptr), "selective_scan: pieces need their scratch");
+    ScanArgs a{B, inner, N, n_slots, ldx, lddt, ldbc, ldz, ldy, NL, vec, 0, piece, scratch,
+               scratch ? scratch + (size_t)n_pieces * inner * N : nullptr,
+               scratch ? scratch + (size_t)n_pieces * inner * (N + 1) : nullptr};
     const VecRef bias{dt_bias, w_dtype}, al{A_log, w_dtype}, dv{Dv, w_dtype};
-    const dim3 grid(ceil_div(inner, SCAN_THREADS / NL), B);
+    dim3 grid(ceil_div(inner, SCAN_THREADS / NL), B);
     const size_t smem = sizeof(float) * ((size_t)8 * SCAN_TB * (SCAN_THREADS / NL) + (size_t)4 * SCAN_TB * (SCAN_R + 4) * NL);
+    auto launch_once = [&]() -> int {
 #define SCAN_LAUNCH(TX, TD)                                                                                              \
     if (smem > 48 * 1024 &&                                                                                              \
         cudaFuncSetAttribute(selective_scan_kernel<TX, TD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
         return mynah_fail("selective_scan: %zu bytes of shared memory are not to be had", smem);                        \
     mynah_launch(selective_scan_kernel<TX, TD>, grid, dim3(2 * SCAN_THREADS), smem, stream, (const TX*)x, dt_raw, bias, al, \
                  dv, (const TD*)Bm, (const TD*)Cm, (const TX*)z, state, (TX*)y, cu_q, slots, a)
-    if (act_dtype == MYNAH_F32 && proj_dtype == MYNAH_F32) { SCAN_LAUNCH(float, float); }
-    else if (act_dtype == MYNAH_BF16 && proj_dtype == MYNAH_F32) { SCAN_LAUNCH(bf16, float); }
-    else if (act_dtype == MYNAH_BF16 && proj_dtype == MYNAH_BF16) { SCAN_LAUNCH(bf16, bf16); }
-    else return mynah_fail("selective_scan: unsupported dtypes %d, %d", act_dtype, proj_dtype);
+        if (act_dtype == MYNAH_F32 && proj_dtype == MYNAH_F32) { SCAN_LAUNCH(float, float); }
+        else if (act_dtype == MYNAH_BF16 && proj_dtype == MYNAH_F32) { SCAN_LAUNCH(bf16, float); }
+        else if (act_dtype == MYNAH_BF16 && proj_dtype == MYNAH_BF16) { SCAN_LAUNCH(bf16, bf16); }
+        else return mynah_fail("selective_scan: unsupported dtypes %d, %d", act_dtype, proj_dtype);
 #undef SCAN_LAUNCH
-    return mynah_check_launch("selective_scan");
+        return mynah_check_launch("selective_scan");
+    };
+    if (piece == 0) return launch_once();
+    MYNAH_REQUIRE(max_q_len > 0 && ceil_div(max_q_len, piece) <= 65535, "selective_scan: too many pieces a sequence");
+    grid.z = ceil_div(max_q_len, piece);
+    a.mode = 1;
+    if (launch_once()) return -1;
+    a.mode = 2;
+    return launch_once();
 }

@@ -677,6 +677,10 @@ def _rows(t: torch.Tensor, name: str) -> None:
         raise KernelError(f"{name} must be rows on the device (unit stride along a row)")
 
 
+# Rows of a piece of the selective scan's two-pass form (0: every sequence is walked whole by one CTA).
+SCAN_PIECE_ROWS = int(os.environ.get("MYNAH_SCAN_PIECE_ROWS", "64"))
+
+
 def selective_scan(x: torch.Tensor, z: torch.Tensor, dt_raw: torch.Tensor, Bm: torch.Tensor, Cm: torch.Tensor,
                    dt_bias, A_log: torch.Tensor, D, state: torch.Tensor, ctx) -> torch.Tensor:
     """The Mamba-1 recurrence with its gate (csrc/selective_scan.cu). x, z [T, inner] (z may be a column slice);
@@ -693,10 +697,16 @@ def selective_scan(x: torch.Tensor, z: torch.Tensor, dt_raw: torch.Tensor, Bm: t
     if A_log.dtype != dt_bias.dtype or A_log.dtype != D.dtype:
         raise KernelError("selective_scan: A_log, dt bias and D must share a dtype")
     y = torch.empty((T, inner), dtype=x.dtype, device=x.device)
+    # Prompts of at least two pieces run piece by piece, side by side, in two passes (see the kernel); the pieces'
+    # end states and the sums of their step sizes go through scratch memory.
+    piece = SCAN_PIECE_ROWS if (not ctx.is_decode and SCAN_PIECE_ROWS and ctx.max_q_len >= 2 * SCAN_PIECE_ROWS) else 0
+    n_pieces = T // piece + ctx.B + 1 if piece else 0
+    scratch = (torch.empty((n_pieces * inner * (N + 1) + ctx.B * inner * N,), dtype=torch.float32, device=x.device)
+               if piece else None)
     call("mynah_selective_scan", ptr(x), x.stride(0), ptr(z), z.stride(0), ptr(y), inner, code(x.dtype),
          ptr(dt_raw), dt_raw.stride(0), ptr(Bm), ptr(Cm), Bm.stride(0), code(Bm.dtype),
          ptr(dt_bias), ptr(A_log), ptr(D), code(A_log.dtype), ptr(state), state.shape[0] - 1,
-         ptr(ctx.cu_q), ptr(ctx.slots), ctx.B, inner, N, stream_ptr())
+         ptr(ctx.cu_q), ptr(ctx.slots), ctx.B, inner, N, piece, n_pieces, ctx.max_q_len, ptr(scratch), stream_ptr())
     return y
 
 

@@ -104,7 +104,7 @@ _SIGNATURES: dict[str, list] = {
     "mynah_attn_decode_ex": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                              P, P, P, P, P, P, c_int, c_int, c_int, c_float, c_int, P, P, P],
     "mynah_selective_scan": [P, c_int, P, c_int, P, c_int, c_int, P, c_int, P, P, c_int, c_int,
-                             P, P, P, c_int, P, c_int, P, P, c_int, c_int, c_int, P],
+                             P, P, P, c_int, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
     "mynah_delta_prep": [P, c_int, P, P, c_int, c_int, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, P],
     "mynah_delta_rule": [P, P, P, c_int, c_int, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
     "mynah_gated_rmsnorm": [P, P, c_int, c_int, P, c_int, P, c_int, c_int, c_int, c_float, P],

@@ -404,6 +404,7 @@ def test_tensor_core_attention_under_chunks(models):
         close(ref, got_tc, "bfloat16", "tensor-core attention", whole=got_general)
         close(ref, got_general, "bfloat16", "general attention")
     close(ref, run_pieces(engine(models, "wide", "float32"), toks, [150, 151, 400]), "float32", "wide in 32-bit")
+    close(ref, run_pieces(engine(models, "wide", "float32"), toks, []), "float32", "wide in 32-bit, whole")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -424,6 +425,36 @@ def test_first_tokens(models):
         ref = plain.forward(cfg, W, toks)
         assert_close(ref, run_pieces(eng, toks, []), FP32_TOL, f"prompt of {n}")
         assert_close(ref, run_pieces(eng, toks, range(1, n)), FP32_TOL, f"decoded from the first of {n}")
+
+
+def test_long_prompts_in_pieces_side_by_side(models):
+    """Prompts long enough for the scan's two-pass form (pieces that run side by side), alone and in an unequal
+    batch, against the plain implementation and against the one-pass form."""
+    from mynah_slm_b200.ops import kernels
+    _, cfg, W = models["hybrid"]
+    eng = engine(models, "hybrid", "float32")
+    seqs = [tokens_for(cfg, n, 500 + n) for n in (300, 129, 5, 191)]
+    refs = [plain.forward(cfg, W, s) for s in seqs]
+    for s, ref in zip(seqs, refs):
+        close(ref, run_pieces(eng, s, []), "float32", f"whole prompt of {len(s)}")
+        close(ref, run_pieces(eng, s, [len(s) - 140]), "float32", f"prompt of {len(s)} in two pieces")
+    slots = [eng.open_sequence() for _ in seqs]
+    out = eng.step([entry(sl, s, range(len(s))) for sl, s in zip(slots, seqs)]).cpu().numpy()
+    nxt = eng.step([entry(sl, [7], (0,)) for sl in slots]).cpu().numpy()        # the state the prompts left
+    for sl in slots:
+        eng.close_sequence(sl)
+    at = 0
+    for i, (s, ref) in enumerate(zip(seqs, refs)):
+        close(ref, out[at:at + len(s)], "float32", f"batched prompt of {len(s)}")
+        close(plain.forward(cfg, W, s + [7])[-1:], nxt[i:i + 1], "float32", f"the token after the prompt of {len(s)}")
+        at += len(s)
+    before = kernels.SCAN_PIECE_ROWS
+    kernels.SCAN_PIECE_ROWS = 0
+    try:
+        one_pass = run_pieces(engine(models, "hybrid", "float32", use_graphs=False), seqs[0], [])
+    finally:
+        kernels.SCAN_PIECE_ROWS = before
+    assert_close(one_pass, run_pieces(eng, seqs[0], []), 2e-5, "two passes against one")
 
 
 def test_without_graphs_equals_with(models):
