@@ -28,7 +28,11 @@ def main(argv=None) -> int:
 
     from .engine import Engine, StepEntry
     os.makedirs(args.out, exist_ok=True)
-    engine = Engine.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens, device=args.device)
+    # A page holds 64 positions of ONE request, so live requests that hold --max-tokens tokens between them may need up
+    # to one page more each than their tokens fill; as many spare pages as there can be such requests (at most 512).
+    spare_pages = min(max(args.max_tokens, 1), 512)
+    engine = Engine.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens + 64 * spare_pages,
+                                device=args.device)
     slots: dict[str, int] = {}
     for line in sys.stdin:
         line = line.strip()

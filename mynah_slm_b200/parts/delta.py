@@ -44,6 +44,8 @@ class GatedDelta(Mixer):
         self.names = {k: str(spec[k]) for k in _NAMES}
         if self.H % self.G:
             raise ConfigError(f"gated_delta: {self.H} heads are not a multiple of {self.G} q/k heads")
+        if self.dim > 512:
+            raise ConfigError(f"gated_delta: keys of {self.dim} values exceed the 512 that the recurrence kernel stages")
         self.n_qk = 2 * self.G * self.dim
         self.n_conv = self.n_qk + self.H * self.vd
 

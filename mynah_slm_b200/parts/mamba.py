@@ -35,6 +35,9 @@ class Mamba1(Mixer):
         g = lambda k: int(spec[k])
         self.D, self.inner, self.N, self.R, self.taps = g("hidden_size"), g("inner"), g("state"), g("dt_rank"), g("conv")
         self.names = {k: str(spec[k]) for k in _NAMES}
+        if self.N > 256:
+            from ..config.keys import ConfigError
+            raise ConfigError(f"mamba1: a state of {self.N} values a channel exceeds the 256 that the scan kernel holds")
 
     def tensor_specs(self) -> list[TensorSpec]:
         n, D, I, N, R = self.names, self.D, self.inner, self.N, self.R

@@ -113,7 +113,16 @@ WIDE = config(128, 200, [
     with_mlp(attn(4, 2, 64, 64, 0.2, mask=200, v_mix=True), 96),
 ], taps=2, max_positions=700)
 
-CONFIGS = {"wide": WIDE, "hybrid": HYBRID, "odd": ODD, "attention": ONLY_ATTENTION, "mamba": ONLY_MAMBA, "delta": ONLY_DELTA,
+# the large ends: a state of 128 and of 256 values a channel, keys of 256 in the delta rule and in attention (values
+# of 8), six taps in front of the mixers and five inside them, many kv heads
+LARGE = config(96, 180, [
+    with_mlp(mamba(48, 128, 5, 5), None),
+    with_mlp(delta(4, 2, 256, 40, 5), 64),
+    with_mlp(attn(8, 8, 256, 8, 0.06, rot=(128, 10000.0), mask=90), None),
+    with_mlp(mamba(40, 256, 3, 2), None),
+], taps=6, max_positions=320)
+
+CONFIGS = {"wide": WIDE, "large": LARGE, "hybrid": HYBRID, "odd": ODD, "attention": ONLY_ATTENTION, "mamba": ONLY_MAMBA, "delta": ONLY_DELTA,
            "mlp": ONLY_MLP, "sharp": SHARP}
 
 
@@ -425,6 +434,18 @@ def test_first_tokens(models):
         ref = plain.forward(cfg, W, toks)
         assert_close(ref, run_pieces(eng, toks, []), FP32_TOL, f"prompt of {n}")
         assert_close(ref, run_pieces(eng, toks, range(1, n)), FP32_TOL, f"decoded from the first of {n}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_large_sizes(models, dtype):
+    _, cfg, W = models["large"]
+    eng = engine(models, "large", dtype, max_tokens=1024)
+    toks = tokens_for(cfg, 200, 61)
+    ref = plain.forward(cfg, W, toks)
+    whole = run_pieces(eng, toks, [])
+    close(ref, whole, dtype, f"large {dtype} whole")
+    close(ref, run_pieces(eng, toks, [3, 5, 64, 89, 90, 91, 150] + list(range(180, 200))), dtype, f"large {dtype} pieces",
+          whole=whole)
 
 
 def test_long_prompts_in_pieces_side_by_side(models):
