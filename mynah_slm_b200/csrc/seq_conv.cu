@@ -239,17 +239,19 @@ int launch_conv(const void* x, const VecRef& w, const VecRef& bias, float* state
     const int threads = a.C >= 256 ? 256 : (a.C >= 128 ? 128 : 64);
     const dim3 grid(a.T, ceil_div(a.C, threads));
     auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31) == 0; };
-    if (a.C % 8 == 0 && a.ldx % 8 == 0 && a.ldo % 8 == 0 && al(x) && al(out) && al(state)) {
-        const int t8 = a.C / 8 >= 128 ? 128 : (a.C / 8 >= 64 ? 64 : 32);
-        if (!a.update && a.taps <= CONV_MAXT && a.T >= 4 * CONV_ROWS)
-            mynah_launch(causal_conv8_rows_kernel<TI, TO>, dim3(ceil_div(a.T, CONV_ROWS), ceil_div(a.C / 8, t8)), dim3(t8), 0,
-                         stream, (const TI*)x, w, bias, (const float*)state, (TO*)out, tok_seq, cu_q, slots, a);
-        else
+    const bool vec8 = a.C % 8 == 0 && a.ldx % 8 == 0 && a.ldo % 8 == 0 && al(x) && al(out) && al(state);
+    const int t8 = a.C / 8 >= 128 ? 128 : (a.C / 8 >= 64 ? 64 : 32);
+    if (vec8 && !a.update && a.taps <= CONV_MAXT && a.T >= 4 * CONV_ROWS) {
+        // a prompt step: rows slide through registers
+        mynah_launch(causal_conv8_rows_kernel<TI, TO>, dim3(ceil_div(a.T, CONV_ROWS), ceil_div(a.C / 8, t8)), dim3(t8), 0,
+                     stream, (const TI*)x, w, bias, (const float*)state, (TO*)out, tok_seq, cu_q, slots, a);
+    } else if (vec8) {
         mynah_launch(causal_conv8_kernel<TI, TO>, dim3(a.T, ceil_div(a.C / 8, t8)), dim3(t8), 0, stream, (const TI*)x, w, bias,
                      state, (TO*)out, tok_seq, cu_q, slots, a);
-    } else
-    mynah_launch(causal_conv_kernel<TI, TO>, grid, dim3(threads), 0, stream, (const TI*)x, w, bias, state, (TO*)out,
-                 tok_seq, cu_q, slots, a);
+    } else {
+        mynah_launch(causal_conv_kernel<TI, TO>, grid, dim3(threads), 0, stream, (const TI*)x, w, bias, state, (TO*)out,
+                     tok_seq, cu_q, slots, a);
+    }
     if (mynah_check_launch("causal_conv")) return -1;
     if (!a.update && a.taps > 1) {
         conv_state_shift_kernel<TI><<<dim3(ceil_div(a.C, threads), a.B), threads, 0, stream>>>((const TI*)x, state, cu_q, slots, a);
