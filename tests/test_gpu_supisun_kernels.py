@@ -129,25 +129,27 @@ def test_selective_scan(inner, N, piece):
     assert float(state[1].abs().max()) == 0 and float(state[3].abs().max()) == 0
 
 
-@pytest.mark.parametrize("H,G,dim,vd", [(4, 2, 64, 32), (3, 3, 12, 20), (2, 1, 136, 8)])
+@pytest.mark.parametrize("H,G,dim,vd", [(4, 2, 64, 32), (3, 3, 12, 20), (2, 1, 136, 8), (2, 2, 30, 7)])
 def test_delta_rule_and_gated_norm(H, G, dim, vd):
     from mynah_slm_b200.ops import kernels
     rng = np.random.default_rng(dim)
-    lens = [45, 3]
+    lens = [45, 3, 33]
     T = sum(lens)
     unit = lambda a: a / np.sqrt((a * a).sum(-1, keepdims=True) + 1e-6)
     qn = unit(rng.normal(size=(T, G, dim))) * dim ** -0.5
     kn = unit(rng.normal(size=(T, G, dim)))
     v = rng.normal(size=(T, H, vd))
     g, beta = rng.uniform(0.5, 1.0, (T, H)), rng.uniform(0.1, 0.9, (T, H))
-    state = torch.zeros((3, H, dim, vd), dtype=torch.float32, device=DEV)
-    ctx = ctx_for(lens, [1, 0])
-    o = kernels.delta_rule(t32(qn.reshape(T, -1)), t32(kn.reshape(T, -1)), t32(v.reshape(T, -1)), t32(g), t32(beta), state, ctx,
-                           H, G, dim, vd).cpu().numpy().reshape(T, H, vd)
+    state = t32(0.3 * rng.normal(size=(4, H, dim, vd)))          # the sequences go on from states that are not zero
+    state0 = state.cpu().numpy().copy()
+    slots = [1, 0, 3][:len(lens)]
+    ctx = ctx_for(lens, slots)
+    o = kernels.delta_rule(t32(qn.reshape(T, -1)), t32(kn.reshape(T, -1)), t32(v.reshape(T, -1)), t32(g), t32(beta), state,
+                           ctx, H, G, dim, vd).cpu().numpy().reshape(T, H, vd)
     at = 0
-    for n, slot in zip(lens, (1, 0)):
+    for n, slot in zip(lens, slots):
         for h in range(H):
-            S = np.zeros((dim, vd))
+            S = state0[slot, h].astype(np.float64)
             for t in range(at, at + n):
                 kk, qq = kn[t, h // (H // G)], qn[t, h // (H // G)]
                 S = g[t, h] * S
