@@ -201,30 +201,40 @@ MYNAH_API int mynah_layernorm_rows(const float* x, const int* rows, const void* 
     return mynah_check_launch("layernorm_rows");
 }
 
-// x[r, :] += LN(y[r, :]) for r < n; y [n, ldy] in y_dtype; x fp32 [n, D]; x_copy (null or [n, D] in y_dtype)
-// receives the new x.
+// x[r, :] += LN(y[r, :]) for r < n; y [n, ldy] in y_dtype; x fp32 [n, D]; x_copy (null or [n, D] in copy_dtype)
+// receives the new x. A bfloat16 run may hand y over in fp32 (the product's accumulators, unrounded) and still ask
+// for a bfloat16 copy.
 MYNAH_API int mynah_layernorm_add(const void* y, int y_dtype, int ldy, const void* w, const void* b, int w_dtype,
-                                  float* x, void* x_copy, int n, int D, float eps, cudaStream_t stream) {
+                                  float* x, void* x_copy, int copy_dtype, int n, int D, float eps, cudaStream_t stream) {
     if (n == 0) return 0;
     MYNAH_REQUIRE(n > 0 && D > 0 && ldy >= D, "layernorm_add: bad sizes n=%d D=%d ldy=%d", n, D, ldy);
     const VecRef wv{w, w_dtype}, bv{b, w_dtype};
-    if (vec8_ok(D, ldy, y, w, b, x, x_copy) && (y_dtype == MYNAH_F32 || y_dtype == MYNAH_BF16)) {
+    if (x_copy == nullptr) copy_dtype = y_dtype;
+    const int combo = y_dtype == MYNAH_F32 && copy_dtype == MYNAH_F32 ? 0
+                      : (y_dtype == MYNAH_BF16 && copy_dtype == MYNAH_BF16 ? 1
+                         : (y_dtype == MYNAH_F32 && copy_dtype == MYNAH_BF16 ? 2 : -1));
+    MYNAH_REQUIRE(combo >= 0, "layernorm_add: unsupported dtypes %d -> %d", y_dtype, copy_dtype);
+    if (vec8_ok(D, ldy, y, w, b, x, x_copy)) {
         const int threads = (D / 8 + 31) / 32 * 32;
-        if (y_dtype == MYNAH_F32)
+        if (combo == 0)
             mynah_launch(layernorm_add8_kernel<float, float>, dim3(n), dim3(threads), 0, stream, (const float*)y, ldy, wv, bv,
                          x, (float*)x_copy, D, eps);
-        else
+        else if (combo == 1)
             mynah_launch(layernorm_add8_kernel<bf16, bf16>, dim3(n), dim3(threads), 0, stream, (const bf16*)y, ldy, wv, bv,
+                         x, (bf16*)x_copy, D, eps);
+        else
+            mynah_launch(layernorm_add8_kernel<float, bf16>, dim3(n), dim3(threads), 0, stream, (const float*)y, ldy, wv, bv,
                          x, (bf16*)x_copy, D, eps);
         return mynah_check_launch("layernorm_add");
     }
-    if (y_dtype == MYNAH_F32)
+    if (combo == 0)
         mynah_launch(layernorm_add_kernel<float, float>, dim3(n), dim3(LN_THREADS), 0, stream, (const float*)y, ldy, wv, bv,
                      x, (float*)x_copy, D, eps);
-    else if (y_dtype == MYNAH_BF16)
+    else if (combo == 1)
         mynah_launch(layernorm_add_kernel<bf16, bf16>, dim3(n), dim3(LN_THREADS), 0, stream, (const bf16*)y, ldy, wv, bv,
                      x, (bf16*)x_copy, D, eps);
     else
-        return mynah_fail("layernorm_add: unsupported dtype %d", y_dtype);
+        mynah_launch(layernorm_add_kernel<float, bf16>, dim3(n), dim3(LN_THREADS), 0, stream, (const float*)y, ldy, wv, bv,
+                     x, (bf16*)x_copy, D, eps);
     return mynah_check_launch("layernorm_add");
 }

@@ -570,8 +570,9 @@ def layernorm_rows(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], 
 
 
 def layernorm_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float,
-                  copy: bool = False) -> Optional[torch.Tensor]:
-    """x += LN(y) * w + b, row by row (x fp32, in place). With `copy` the new x is also returned in y's type."""
+                  copy: bool = False, copy_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """x += LN(y) * w + b, row by row (x fp32, in place). With `copy` the new x is also returned, in `copy_dtype`
+    (y's type unless given; an fp32 y may come with a bfloat16 copy)."""
     _chk(x, "residual", torch.float32, 2)
     if y.dim() != 2 or y.stride(1) != 1 or not y.is_cuda:
         raise KernelError("layernorm_add: the sublayer's output must be rows on the device")
@@ -581,9 +582,10 @@ def layernorm_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, b: Optional
     if b is not None:
         _chk(b, "norm bias", w.dtype, 1)
     n, D = x.shape
-    xc = torch.empty((n, D), dtype=y.dtype, device=x.device) if copy else None
+    copy_dtype = copy_dtype or y.dtype
+    xc = torch.empty((n, D), dtype=copy_dtype, device=x.device) if copy else None
     call("mynah_layernorm_add", ptr(y), code(y.dtype), y.stride(0), ptr(w), ptr(b), code(w.dtype), ptr(x), ptr(xc),
-         n, D, float(eps), stream_ptr())
+         code(copy_dtype), n, D, float(eps), stream_ptr())
     return xc
 
 

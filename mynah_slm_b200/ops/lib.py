@@ -89,7 +89,7 @@ _SIGNATURES: dict[str, list] = {
     "mynah_activation": [P, P, c_int, c_longlong, c_int, P],
     "mynah_cast_f32": [P, P, c_int, c_longlong, P],
     "mynah_layernorm_rows": [P, P, P, P, c_int, P, c_int, c_int, c_int, c_float, P],
-    "mynah_layernorm_add": [P, c_int, c_int, P, P, c_int, P, P, c_int, c_int, c_float, P],
+    "mynah_layernorm_add": [P, c_int, c_int, P, P, c_int, P, P, c_int, c_int, c_int, c_float, P],
     "mynah_causal_conv": [P, c_int, c_int, P, P, c_int, P, c_int, P, c_int, c_int, P, P, P,
                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, P],
     "mynah_attn_prep": [P, c_int, c_int, c_int, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,

@@ -140,7 +140,7 @@ class ProjNormAttention(Mixer):
         else:
             attention_dispatch.prefill_masked(q, out, ctx, H, G, dimp, vdp, cache.k, cache.v, pages, self.window or 0,
                                               self.chunk or 0, self.scale)
-        return kernels.linear(out, self.w_o)
+        return kernels.linear(out, self.w_o, out_dtype=torch.float32)      # unrounded into the norm that follows
 
 
 register_mixer("projnorm_attention", ProjNormAttention)

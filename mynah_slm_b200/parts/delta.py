@@ -95,7 +95,7 @@ class GatedDelta(Mixer):
                                              self.A_log, self.dt_bias, H, G, dim)
         o = kernels.delta_rule(qn, kn, qkv[:, self.n_qk:], g, beta, cache.state["S"], ctx, H, G, dim, vd)
         out = kernels.gated_rmsnorm(o, p[:, c0:c1], self.norm_w, H, vd, self.eps)
-        return kernels.linear(out, self.w_o)
+        return kernels.linear(out, self.w_o, out_dtype=torch.float32)      # unrounded into the norm that follows
 
 
 register_mixer("gated_delta", GatedDelta)

@@ -40,7 +40,7 @@ class DenseMLP(FeedForward):
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
         u = kernels.linear(h, self.w_up)
         kernels.activation(u, self.act, out=u)
-        return kernels.linear(u, self.w_down)
+        return kernels.linear(u, self.w_down, out_dtype=torch.float32)     # unrounded into the norm that follows
 
 
 register_ffn("dense_mlp", DenseMLP)

@@ -79,7 +79,7 @@ class Mamba1(Mixer):
         dt_raw = kernels.linear(dbc[:, :R], self.w_dt, out_dtype=torch.float32)
         y = kernels.selective_scan(x, xz[:, I:], dt_raw, dbc[:, R:R + N], dbc[:, R + N:], self.dt_b, self.A_log, self.Dv,
                                    cache.state["scan"], ctx)
-        return kernels.linear(y, self.w_o)
+        return kernels.linear(y, self.w_o, out_dtype=torch.float32)        # unrounded into the norm that follows
 
 
 register_mixer("mamba1", Mamba1)

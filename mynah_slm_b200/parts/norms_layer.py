@@ -4,6 +4,11 @@ out = (x - mean) / sqrt(var + eps) * w + b, with var the mean of the squared
 deviations; fp32 throughout. Parameters: eps, dim, the weight's tensor name
 and the bias's (`bias`; None: no bias).
 
+A sublayer whose output goes straight into `add_normed` does well to hand it
+over in fp32 (its last product's accumulators, unrounded): the norm subtracts the
+row's mean, and where the mean is large against the spread, a bfloat16 rounding
+of the output would be magnified by that ratio.
+
 It serves both placements: `apply` norms rows of the residual stream (a
 model's last norm, or a pre-norm block), and `add_normed` norms a sublayer's
 OUTPUT and adds it to the stream, x <- x + LN(y), for blocks that norm
@@ -48,7 +53,7 @@ class LayerNorm(Norm):
     def add_normed(self, stream: Residual, y: torch.Tensor, copy: bool = False) -> Optional[torch.Tensor]:
         """x <- x + LN(y); with `copy` also returns the new x in the activation type."""
         x = stream.flush()
-        return kernels.layernorm_add(x, y, self.weight, self.bias, self.eps, copy=copy)
+        return kernels.layernorm_add(x, y, self.weight, self.bias, self.eps, copy=copy, copy_dtype=self.act_dtype)
 
 
 register_norm("layernorm", LayerNorm)

@@ -140,7 +140,7 @@ def test_delta_rule_and_gated_norm(H, G, dim, vd):
     kn = unit(rng.normal(size=(T, G, dim)))
     v = rng.normal(size=(T, H, vd))
     g, beta = rng.uniform(0.5, 1.0, (T, H)), rng.uniform(0.1, 0.9, (T, H))
-    state = t32(0.3 * rng.normal(size=(4, H, dim, vd)))          # the sequences go on from states that are not zero
+    state = t32(0.3 * rng.normal(size=(5, H, dim, vd)))          # the sequences go on from states that are not zero; the last row is no slot's
     state0 = state.cpu().numpy().copy()
     slots = [1, 0, 3][:len(lens)]
     ctx = ctx_for(lens, slots)
