@@ -8,10 +8,11 @@
 #include "head_prep.cuh"
 
 // ------------------------------------------------------------- embedding
-// x[t, :] = E[token_t, :]           (mynah-slm src/arch_qwen3.c:186: no scaling)
+// x[t, :] = E[token_t, :] * scale   (mynah-slm src/arch_qwen3.c:186 has no scaling: scale 1; a design that
+// multiplies its embedding by a constant gives it here; the product is fp32)
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
-                                    float* __restrict__ x, int D, int V) {
+                                    float* __restrict__ x, int D, int V, float scale) {
     griddep_launch();
     griddep_wait();
     const int t = blockIdx.x;
@@ -22,32 +23,32 @@ __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __r
         return;
     }
     const TW* row = table + (size_t)tok * D;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) out[i] = to_f32(row[i]);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) out[i] = to_f32(row[i]) * scale;
 }
 
 MYNAH_API int mynah_embed_gather(const void* table, int table_dtype, const int* tokens, float* x,
-                                 int T, int D, int V, cudaStream_t stream) {
+                                 int T, int D, int V, float scale, cudaStream_t stream) {
     if (T == 0) return 0;
     MYNAH_REQUIRE(T > 0 && D > 0 && V > 0, "embed_gather: bad sizes T=%d D=%d V=%d", T, D, V);
     const int threads = D >= 1024 ? 256 : (D >= 256 ? 128 : 64);
     if (table_dtype == MYNAH_F32)
-        mynah_launch(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, tokens, x, D, V);
+        mynah_launch(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, tokens, x, D, V, scale);
     else if (table_dtype == MYNAH_BF16)
-        mynah_launch(embed_gather_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)table, tokens, x, D, V);
+        mynah_launch(embed_gather_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)table, tokens, x, D, V, scale);
     else
         return mynah_fail("embed_gather: unsupported table dtype %d", table_dtype);
     return mynah_check_launch("embed_gather");
 }
 
 // --------------------------------------------------------------- RMSNorm
-// v = x[r] (+ delta[r]);  x[r] = v when delta is given and every row is taken (no `rows`);
+// v = x[r] (+ dscale * delta[r]);  x[r] = v when delta is given and every row is taken (no `rows`);
 // out[i] = (v * s) * w   with   s = 1 / sqrt(mean(v^2) + eps)
 // (mynah-slm src/kernels.c:118-128; plain gain, not 1+w). `rows`, when given,
 // selects the rows to normalise (the rows whose logits are wanted); out then
 // has one row per selected row.
 template <typename TA>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ delta, VecRef w,
-                               const int* __restrict__ rows, TA* __restrict__ out, int D, float eps) {
+                               const int* __restrict__ rows, TA* __restrict__ out, int D, float eps, float dscale) {
     __shared__ float red[32];
     griddep_launch_small();
     griddep_wait();
@@ -61,7 +62,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ del
     for (int i = threadIdx.x; i < D; i += blockDim.x) {
         float v = xr[i];
         if (dr) {
-            v += to_f32(dr[i]);
+            v += to_f32(dr[i]) * dscale;
             if (keep) xr[i] = v;
         }
         ss += v * v;
@@ -71,7 +72,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ del
     TA* o = out + (size_t)blockIdx.x * D;
     for (int i = threadIdx.x; i < D; i += blockDim.x) {
         float v = xr[i];
-        if (dr && !keep) v += to_f32(dr[i]);
+        if (dr && !keep) v += to_f32(dr[i]) * dscale;
         o[i] = from_f32<TA>((v * s) * w.at(i));
     }
 }
@@ -80,7 +81,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ del
 // memory. Taken when D is a multiple of 4 and fits (D <= 4 * 1024).
 template <typename TA>
 __global__ void rmsnorm_vec4_kernel(float* __restrict__ x, const TA* __restrict__ delta, VecRef w,
-                                    const int* __restrict__ rows, TA* __restrict__ out, int D, float eps) {
+                                    const int* __restrict__ rows, TA* __restrict__ out, int D, float eps, float dscale) {
     __shared__ float red[32];
     griddep_launch_small();
     griddep_wait();
@@ -93,7 +94,7 @@ __global__ void rmsnorm_vec4_kernel(float* __restrict__ x, const TA* __restrict_
         v = *reinterpret_cast<const float4*>(xr + i);
         if (delta) {
             const TA* dr = delta + (size_t)r * D + i;
-            v.x += to_f32(dr[0]); v.y += to_f32(dr[1]); v.z += to_f32(dr[2]); v.w += to_f32(dr[3]);
+            v.x += to_f32(dr[0]) * dscale; v.y += to_f32(dr[1]) * dscale; v.z += to_f32(dr[2]) * dscale; v.w += to_f32(dr[3]) * dscale;
             if (rows == nullptr) *reinterpret_cast<float4*>(xr + i) = v;     // (selected rows may repeat: x is only read)
         }
     }
@@ -114,7 +115,7 @@ __global__ void rmsnorm_vec4_kernel(float* __restrict__ x, const TA* __restrict_
 // has the same order in every step.
 template <typename TA>
 __global__ void rmsnorm_vec8_kernel(float* __restrict__ x, const TA* __restrict__ delta, VecRef w,
-                                    const int* __restrict__ rows, TA* __restrict__ out, int D, float eps) {
+                                    const int* __restrict__ rows, TA* __restrict__ out, int D, float eps, float dscale) {
     __shared__ float red[32];
     griddep_launch_small();
     griddep_wait();
@@ -129,7 +130,7 @@ __global__ void rmsnorm_vec8_kernel(float* __restrict__ x, const TA* __restrict_
             float d[8];
             load8(delta + (size_t)r * D + i, d);
 #pragma unroll
-            for (int j = 0; j < 8; j++) v[j] += d[j];
+            for (int j = 0; j < 8; j++) v[j] += d[j] * dscale;
             if (rows == nullptr) store8(xr + i, v);        // (selected rows may repeat: x is only read)
         }
     }
@@ -146,7 +147,7 @@ __global__ void rmsnorm_vec8_kernel(float* __restrict__ x, const TA* __restrict_
 }
 
 MYNAH_API int mynah_rmsnorm(float* x, const void* delta, const void* w, int w_dtype, const int* rows,
-                            void* out, int act_dtype, int n_rows, int D, float eps, cudaStream_t stream) {
+                            void* out, int act_dtype, int n_rows, int D, float eps, float dscale, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     MYNAH_REQUIRE(n_rows > 0 && D > 0, "rmsnorm: bad sizes rows=%d D=%d", n_rows, D);
     MYNAH_REQUIRE(w_dtype == MYNAH_F32 || w_dtype == MYNAH_BF16, "rmsnorm: unsupported gain dtype %d", w_dtype);
@@ -155,9 +156,9 @@ MYNAH_API int mynah_rmsnorm(float* x, const void* delta, const void* w, int w_dt
     if (D % 8 == 0 && D <= 8192 && D >= 256 && aligned16) {
         const int threads = ((D / 8 + 31) / 32) * 32;
         if (act_dtype == MYNAH_F32)
-            mynah_launch(rmsnorm_vec8_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, (const float*)delta, wr, rows, (float*)out, D, eps);
+            mynah_launch(rmsnorm_vec8_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, (const float*)delta, wr, rows, (float*)out, D, eps, dscale);
         else if (act_dtype == MYNAH_BF16)
-            mynah_launch(rmsnorm_vec8_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, (const bf16*)delta, wr, rows, (bf16*)out, D, eps);
+            mynah_launch(rmsnorm_vec8_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, (const bf16*)delta, wr, rows, (bf16*)out, D, eps, dscale);
         else
             return mynah_fail("rmsnorm: unsupported activation dtype %d", act_dtype);
         return mynah_check_launch("rmsnorm");
@@ -165,18 +166,18 @@ MYNAH_API int mynah_rmsnorm(float* x, const void* delta, const void* w, int w_dt
     if (D % 4 == 0 && D <= 4096 && D >= 128) {
         const int threads = ((D / 4 + 31) / 32) * 32;
         if (act_dtype == MYNAH_F32)
-            mynah_launch(rmsnorm_vec4_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, (const float*)delta, wr, rows, (float*)out, D, eps);
+            mynah_launch(rmsnorm_vec4_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, (const float*)delta, wr, rows, (float*)out, D, eps, dscale);
         else if (act_dtype == MYNAH_BF16)
-            mynah_launch(rmsnorm_vec4_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, (const bf16*)delta, wr, rows, (bf16*)out, D, eps);
+            mynah_launch(rmsnorm_vec4_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, (const bf16*)delta, wr, rows, (bf16*)out, D, eps, dscale);
         else
             return mynah_fail("rmsnorm: unsupported activation dtype %d", act_dtype);
         return mynah_check_launch("rmsnorm");
     }
     const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : (D >= 128 ? 128 : 32));
     if (act_dtype == MYNAH_F32)
-        mynah_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, (const float*)delta, wr, rows, (float*)out, D, eps);
+        mynah_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, (const float*)delta, wr, rows, (float*)out, D, eps, dscale);
     else if (act_dtype == MYNAH_BF16)
-        mynah_launch(rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, (const bf16*)delta, wr, rows, (bf16*)out, D, eps);
+        mynah_launch(rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, (const bf16*)delta, wr, rows, (bf16*)out, D, eps, dscale);
     else
         return mynah_fail("rmsnorm: unsupported activation dtype %d", act_dtype);
     return mynah_check_launch("rmsnorm");
@@ -184,20 +185,20 @@ MYNAH_API int mynah_rmsnorm(float* x, const void* delta, const void* w, int w_dt
 
 // ----------------------------------------------------------- residual add
 template <typename TA>
-__global__ void residual_add_kernel(float* __restrict__ x, const TA* __restrict__ delta, size_t n) {
+__global__ void residual_add_kernel(float* __restrict__ x, const TA* __restrict__ delta, size_t n, float scale) {
     griddep_launch();
     griddep_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) x[i] += to_f32(delta[i]);          // mynah-slm src/kernels.c:222-224
+    if (i < n) x[i] += to_f32(delta[i]) * scale;  // mynah-slm src/kernels.c:222-224 (scale 1 there)
 }
 
-MYNAH_API int mynah_residual_add(float* x, const void* delta, int act_dtype, long long n, cudaStream_t stream) {
+MYNAH_API int mynah_residual_add(float* x, const void* delta, int act_dtype, long long n, float scale, cudaStream_t stream) {
     if (n == 0) return 0;
     const unsigned blocks = (unsigned)ceil_div_ll(n, 256);
     if (act_dtype == MYNAH_F32)
-        mynah_launch(residual_add_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, (const float*)delta, (size_t)n);
+        mynah_launch(residual_add_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, (const float*)delta, (size_t)n, scale);
     else if (act_dtype == MYNAH_BF16)
-        mynah_launch(residual_add_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, x, (const bf16*)delta, (size_t)n);
+        mynah_launch(residual_add_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, x, (const bf16*)delta, (size_t)n, scale);
     else
         return mynah_fail("residual_add: unsupported activation dtype %d", act_dtype);
     return mynah_check_launch("residual_add");
@@ -307,13 +308,14 @@ MYNAH_API int mynah_embed_positions(const void* table, const void* pos_table, in
 
 // ------------------------------------------------------------ activations
 // In place or not: out[i] = act(in[i]), computed in fp32. 0: gelu with erf, 0.5 z (1 + erf(z / sqrt 2));
-// 1: gelu with tanh, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 2: silu; 3: relu.
+// 1: gelu with tanh, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 2: silu; 3: relu; 4: the square of relu.
 __device__ __forceinline__ float act_apply(float z, int act) {
     switch (act) {
         case 0: return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
         case 1: return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
         case 2: return z / (1.0f + expf(-z));
-        default: return fmaxf(z, 0.f);
+        case 3: return fmaxf(z, 0.f);
+        default: { const float r = fmaxf(z, 0.f); return r * r; }
     }
 }
 
@@ -341,7 +343,7 @@ __global__ void activation8_kernel(const T* __restrict__ in, T* __restrict__ out
 
 MYNAH_API int mynah_activation(const void* in, void* out, int dtype, long long n, int act, cudaStream_t stream) {
     if (n == 0) return 0;
-    MYNAH_REQUIRE(n > 0 && act >= 0 && act <= 3, "activation: bad arguments n=%lld act=%d", n, act);
+    MYNAH_REQUIRE(n > 0 && act >= 0 && act <= 4, "activation: bad arguments n=%lld act=%d", n, act);
     if (n % 8 == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 31) == 0 &&
         (dtype == MYNAH_F32 || dtype == MYNAH_BF16)) {
         const long long n8 = n / 8;
@@ -384,4 +386,20 @@ MYNAH_API int mynah_cast_f32(const float* in, void* out, int out_dtype, long lon
     else
         return mynah_fail("cast_f32: unsupported dtype %d", out_dtype);
     return mynah_check_launch("cast_f32");
+}
+
+// ----------------------------------------------------------------- scale
+// x[i] *= s in place (fp32): a head whose logits are multiplied by a constant.
+__global__ void scale_f32_kernel(float* __restrict__ x, long long n, float s) {
+    griddep_launch_small();
+    griddep_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] *= s;
+}
+
+MYNAH_API int mynah_scale_f32(float* x, long long n, float s, cudaStream_t stream) {
+    if (n == 0) return 0;
+    MYNAH_REQUIRE(n > 0, "scale_f32: bad size %lld", n);
+    mynah_launch(scale_f32_kernel, dim3((unsigned)ceil_div_ll(n, 256)), dim3(256), 0, stream, x, n, s);
+    return mynah_check_launch("scale_f32");
 }

@@ -1,0 +1,211 @@
+// Feed-forward of several small experts of which every token uses `top`, and the steps around it:
+//
+//   moe_route     a token's experts come from a table indexed by its token id ([vocab][top]); the step's
+//                 (token, choice) pairs are sorted by expert into one list, cut into tiles of rows that share an
+//                 expert. One CTA: count, scan, place. The order inside an expert's list is not fixed, and does
+//                 not matter: a row's arithmetic does not depend on its place in a tile.
+//   moe_gate_up   for every tile: g = min(W_gate,e h, limit), u = clamp(W_up,e h, -limit, limit),
+//                 y = g * sigmoid(alpha g) * (u + 1), written per pair                         (act: clamped)
+//   moe_down      for every tile: W_down,e y, written per pair in fp32
+//   moe_combine   out[t] = weight * sum over the token's pairs, in the order of its choices
+//
+// The grid of the two products covers the most tiles a step can have (pairs / rows-per-tile + experts); CTAs
+// beyond the step's tiles leave at once, so a captured step needs no count from the host.
+#include "layout.cuh"
+#include "tile_mm.cuh"
+
+namespace {
+
+constexpr int MOE_ROUTE_THREADS = 1024;
+constexpr int MOE_MAX_EXPERTS = 1024;
+
+// tiles: [0] number of tiles, then per tile (expert, first index into perm, rows)
+__global__ void __launch_bounds__(MOE_ROUTE_THREADS)
+moe_route_kernel(const int* __restrict__ tokens, const int* __restrict__ tok_seq, const int* __restrict__ table,
+                 int T, int V, int top, int E, int BM, int* __restrict__ pair_expert, int* __restrict__ perm,
+                 int* __restrict__ tiles, int max_tiles, int* __restrict__ status) {
+    __shared__ int count[MOE_MAX_EXPERTS], start[MOE_MAX_EXPERTS];
+    griddep_wait();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    const int P = T * top;
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int t = p / top;
+        int e = -1;
+        if (tok_seq[t] >= 0) {
+            const int tok = tokens[t];
+            if (tok >= 0 && tok < V) e = table[(size_t)tok * top + p % top];
+            if (e < 0 || e >= E) {
+                atomicOr(status, MYNAH_ST_TOKEN_RANGE);
+                e = -1;
+            }
+        }
+        pair_expert[p] = e;
+        if (e >= 0) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, nt = 0;
+        for (int e = 0; e < E; e++) {
+            start[e] = at;
+            for (int r = 0; r < count[e] && nt < max_tiles; r += BM, nt++) {
+                tiles[1 + 3 * nt] = e;
+                tiles[2 + 3 * nt] = at + r;
+                tiles[3 + 3 * nt] = min(BM, count[e] - r);
+            }
+            at += count[e];
+        }
+        tiles[0] = nt;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int e = pair_expert[p];
+        if (e >= 0) perm[start[e] + atomicAdd(&count[e], 1)] = p;
+    }
+}
+
+struct MoeArgs {
+    int top, D, F;
+    float limit, alpha;
+};
+
+// grid (tiles, column tiles of F). h: [T][D] rows; w_gu: [E][2][F][D] (gate rows, then up rows); y: [P][F]
+template <typename TA, int BM>
+__global__ void __launch_bounds__(tilemm::THREADS)
+moe_gate_up_kernel(const TA* __restrict__ h, const TA* __restrict__ w_gu, TA* __restrict__ y,
+                   const int* __restrict__ perm, const int* __restrict__ tiles, MoeArgs a) {
+    constexpr int BN = 64;
+    __shared__ tilemm::Smem<BM, BN> s;
+    __shared__ int pair_s[BM];
+    griddep_wait();
+    if ((int)blockIdx.x >= tiles[0]) return;
+    const int e = tiles[1 + 3 * blockIdx.x], r0 = tiles[2 + 3 * blockIdx.x], nr = tiles[3 + 3 * blockIdx.x];
+    const int c0 = blockIdx.y * BN;
+    for (int i = threadIdx.x; i < BM; i += blockDim.x) {
+        const int p = i < nr ? perm[r0 + i] : -1;
+        pair_s[i] = p;
+        s.rows[i] = p >= 0 ? h + (size_t)(p / a.top) * a.D : nullptr;
+    }
+    const TA* wg = w_gu + ((size_t)e * 2 * a.F + c0) * a.D;
+    float g[BM / 16][BN / 16], u[BM / 16][BN / 16];
+    tilemm::run<TA, BM, BN>(s, wg, (size_t)a.D, a.F - c0, a.D, g);
+    tilemm::run<TA, BM, BN>(s, wg + (size_t)a.F * a.D, (size_t)a.D, a.F - c0, a.D, u);
+    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+#pragma unroll
+    for (int i = 0; i < BM / 16; i++) {
+        const int p = pair_s[ty + 16 * i];
+        if (p < 0) continue;
+#pragma unroll
+        for (int j = 0; j < BN / 16; j++) {
+            const int c = c0 + tx + 16 * j;
+            if (c >= a.F) continue;
+            // the products are rounded to the activation type first, as a product kernel would store them
+            const float gv = fminf(round_to<TA>(g[i][j]), a.limit);
+            const float uv = fminf(fmaxf(round_to<TA>(u[i][j]), -a.limit), a.limit);
+            y[(size_t)p * a.F + c] = from_f32<TA>(gv * (1.0f / (1.0f + expf(-a.alpha * gv))) * (uv + 1.0f));
+        }
+    }
+}
+
+// grid (tiles, column tiles of D). y: [P][F]; w_down: [E][D][F]; o: fp32 [P][D]
+template <typename TA, int BM>
+__global__ void __launch_bounds__(tilemm::THREADS)
+moe_down_kernel(const TA* __restrict__ y, const TA* __restrict__ w_down, float* __restrict__ o,
+                const int* __restrict__ perm, const int* __restrict__ tiles, MoeArgs a) {
+    constexpr int BN = 64;
+    __shared__ tilemm::Smem<BM, BN> s;
+    __shared__ int pair_s[BM];
+    griddep_wait();
+    if ((int)blockIdx.x >= tiles[0]) return;
+    const int e = tiles[1 + 3 * blockIdx.x], r0 = tiles[2 + 3 * blockIdx.x], nr = tiles[3 + 3 * blockIdx.x];
+    const int c0 = blockIdx.y * BN;
+    for (int i = threadIdx.x; i < BM; i += blockDim.x) {
+        const int p = i < nr ? perm[r0 + i] : -1;
+        pair_s[i] = p;
+        s.rows[i] = p >= 0 ? y + (size_t)p * a.F : nullptr;
+    }
+    float acc[BM / 16][BN / 16];
+    tilemm::run<TA, BM, BN>(s, w_down + ((size_t)e * a.D + c0) * a.F, (size_t)a.F, a.D - c0, a.F, acc);
+    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+#pragma unroll
+    for (int i = 0; i < BM / 16; i++) {
+        const int p = pair_s[ty + 16 * i];
+        if (p < 0) continue;
+#pragma unroll
+        for (int j = 0; j < BN / 16; j++) {
+            const int c = c0 + tx + 16 * j;
+            if (c < a.D) o[(size_t)p * a.D + c] = acc[i][j];
+        }
+    }
+}
+
+template <typename TA>
+__global__ void moe_combine_kernel(const float* __restrict__ o, const int* __restrict__ pair_expert, TA* __restrict__ out,
+                                   int top, int D, float weight) {
+    griddep_launch_small();
+    griddep_wait();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; k++) {
+            const int p = t * top + k;
+            if (pair_expert[p] >= 0) acc += o[(size_t)p * D + c];
+        }
+        out[(size_t)t * D + c] = from_f32<TA>(acc * weight);
+    }
+}
+
+template <typename TA, int BM>
+int launch_products(const void* h, const void* w_gu, const void* w_down, void* y, float* o, const int* perm,
+                    const int* tiles, int max_tiles, const MoeArgs& a, cudaStream_t stream) {
+    mynah_launch(moe_gate_up_kernel<TA, BM>, dim3(max_tiles, ceil_div(a.F, 64)), dim3(tilemm::THREADS), 0, stream,
+                 (const TA*)h, (const TA*)w_gu, (TA*)y, perm, tiles, a);
+    if (mynah_check_launch("moe_gate_up") != 0) return -1;
+    mynah_launch(moe_down_kernel<TA, BM>, dim3(max_tiles, ceil_div(a.D, 64)), dim3(tilemm::THREADS), 0, stream,
+                 (const TA*)y, (const TA*)w_down, o, perm, tiles, a);
+    return mynah_check_launch("moe_down");
+}
+
+}  // namespace
+
+// Rows of a tile for a step of T tokens: small steps (decode) take 16-row tiles, prompts 64-row tiles.
+MYNAH_API int mynah_moe_tile_rows(int T, int top) { return (long long)T * top <= 256 ? 16 : 64; }
+
+// Most tiles a step of T tokens can have.
+MYNAH_API int mynah_moe_max_tiles(int T, int top, int E) { return ceil_div(T * top, mynah_moe_tile_rows(T, top)) + E; }
+
+// The whole feed-forward. h: [T][D]; table: int32 [V][top]; w_gu: [E][2][F][D]; w_down: [E][D][F]; out: [T][D] in the
+// activation type. Scratch: y [T*top][F] (activation type), o fp32 [T*top][D], ints [2*T*top + 1 + 3*max_tiles].
+MYNAH_API int mynah_moe_table_ffn(const void* h, int dtype, const int* tokens, const int* tok_seq, const int* table,
+                                  const void* w_gu, const void* w_down, void* out, void* y, float* o, int* ints,
+                                  int T, int V, int top, int E, int D, int F, float limit, float alpha, float weight,
+                                  int* status, cudaStream_t stream) {
+    if (T == 0) return 0;
+    MYNAH_REQUIRE(T > 0 && V > 0 && top > 0 && E > 0 && D > 0 && F > 0, "moe_table_ffn: bad sizes");
+    MYNAH_REQUIRE(E <= MOE_MAX_EXPERTS, "moe_table_ffn: %d experts exceed %d", E, MOE_MAX_EXPERTS);
+    MYNAH_REQUIRE(dtype == MYNAH_F32 || dtype == MYNAH_BF16, "moe_table_ffn: unsupported dtype %d", dtype);
+    const int P = T * top, BM = mynah_moe_tile_rows(T, top), max_tiles = mynah_moe_max_tiles(T, top, E);
+    int* pair_expert = ints;
+    int* perm = ints + P;
+    int* tiles = ints + 2 * P;
+    mynah_launch(moe_route_kernel, dim3(1), dim3(MOE_ROUTE_THREADS), 0, stream, tokens, tok_seq, table, T, V, top, E, BM,
+                 pair_expert, perm, tiles, max_tiles, status);
+    if (mynah_check_launch("moe_route") != 0) return -1;
+    const MoeArgs a{top, D, F, limit, alpha};
+    int rc;
+    if (dtype == MYNAH_F32)
+        rc = BM == 16 ? launch_products<float, 16>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream)
+                      : launch_products<float, 64>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream);
+    else
+        rc = BM == 16 ? launch_products<bf16, 16>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream)
+                      : launch_products<bf16, 64>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream);
+    if (rc != 0) return rc;
+    const int threads = D >= 1024 ? 256 : 128;
+    if (dtype == MYNAH_F32)
+        mynah_launch(moe_combine_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)o, (const int*)pair_expert, (float*)out, top, D, weight);
+    else
+        mynah_launch(moe_combine_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const float*)o, (const int*)pair_expert, (bf16*)out, top, D, weight);
+    return mynah_check_launch("moe_combine");
+}

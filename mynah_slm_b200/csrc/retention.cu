@@ -1,0 +1,198 @@
+// Retention: linear attention with a fixed decay per head, no softmax and no denominator. Per head, with
+// S [dim x vd] the state (fp32, carried per slot):
+//
+//   S_t = decay_h S_(t-1) + k_t v_t^T,      o_t = S_t^T q_t
+//
+// Two kernels (the per-head unit RMS and the gate that follow are `gated_rmsnorm`):
+//
+//   retention_prep   q, k rows -> fp32, the first `rot` dims of every head rotated by the position's table row
+//                    (pairs (i, i + rot/2), or (2i, 2i+1)), k then multiplied by k_scale
+//   retention_scan   the recurrence. The columns of S are independent, so a CTA takes a tile of columns of one
+//                    head of one sequence; a column's dim values lie in the registers of L adjacent lanes (up to
+//                    32 values a lane), which add their parts of o by shuffles in a fixed order. Keys, queries and
+//                    values of 32 tokens at a time pass through shared memory.
+//
+// All arithmetic is fp32. A sequence's rows are walked in order, so a prompt run whole, in pieces or token by
+// token performs the same operations in the same order.
+#include "layout.cuh"
+
+namespace {
+
+struct RetPrepArgs {
+    int H, dim, ld, q_off, k_off;    // heads, head size, row stride, first columns of q and k
+    int rot, interleaved, n_pos;
+    float k_scale;
+};
+
+// one CTA a token
+template <typename T>
+__global__ void __launch_bounds__(128)
+retention_prep_kernel(const T* __restrict__ qk, float* __restrict__ qn, float* __restrict__ kn,
+                      const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                      const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, RetPrepArgs a,
+                      int* __restrict__ status) {
+    griddep_launch_small();
+    griddep_wait();
+    const int t = blockIdx.x;
+    if (tok_seq[t] < 0) return;
+    const int pos = tok_pos[t];
+    const bool rotate = a.rot > 0 && cos_t != nullptr;
+    if (rotate && (pos < 0 || pos >= a.n_pos)) {
+        if (threadIdx.x == 0) atomicOr(status, MYNAH_ST_POS_RANGE);
+        return;
+    }
+    const int half = a.rot >> 1;
+    const float* cr = rotate ? cos_t + (size_t)pos * half : nullptr;
+    const float* sr = rotate ? sin_t + (size_t)pos * half : nullptr;
+    const int n = a.H * a.dim;
+    const T* row = qk + (size_t)t * a.ld;
+    for (int idx = threadIdx.x; idx < 2 * n; idx += blockDim.x) {
+        const bool is_k = idx >= n;
+        const int e = is_k ? idx - n : idx;
+        const int h = e / a.dim, d = e % a.dim;
+        const T* src = row + (is_k ? a.k_off : a.q_off) + (size_t)h * a.dim;
+        float v = to_f32(src[d]);
+        if (rotate && d < a.rot) {
+            int i, other;
+            float sign;
+            if (a.interleaved) {
+                i = d >> 1; other = d ^ 1; sign = (d & 1) ? 1.f : -1.f;
+            } else {
+                i = d < half ? d : d - half; other = d < half ? d + half : d - half; sign = d < half ? -1.f : 1.f;
+            }
+            v = v * cr[i] + sign * to_f32(src[other]) * sr[i];
+        }
+        if (is_k) kn[(size_t)t * n + e] = v * a.k_scale;
+        else qn[(size_t)t * n + e] = v;
+    }
+}
+
+constexpr int RET_THREADS = 128;
+constexpr int RET_TB = 32;                 // tokens staged in shared memory at a time
+constexpr int RET_RMAX = 32;               // state values a lane keeps
+
+struct RetArgs {
+    int B, H, dim, vd, n_slots, ldv, v_off;
+    int L, per;                            // lanes a column (a power of two <= 32), values a lane (<= RET_RMAX)
+};
+
+template <typename T>
+__global__ void __launch_bounds__(RET_THREADS)
+retention_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const T* __restrict__ v,
+                      const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ o,
+                      const int* __restrict__ cu_q, const int* __restrict__ slots, RetArgs a) {
+    extern __shared__ float sm[];
+    griddep_wait();
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int slot = slots[b];
+    const int q0 = cu_q[b], q1 = cu_q[b + 1];
+    if (slot < 0 || slot >= a.n_slots || q1 <= q0) return;
+    const int L = a.L, per = a.per;
+    const int JT = RET_THREADS / L;
+    const int l = threadIdx.x % L, jl = threadIdx.x / L;
+    const int j = blockIdx.x * JT + jl;
+    const bool on = j < a.vd;
+    const int CS = per + 1;                                      // floats of a lane's chunk (padded against bank conflicts)
+    const int rowf = CS * L;
+    float* ks = sm;                                              // [TB][rowf]
+    float* qs = ks + RET_TB * rowf;                              // [TB][rowf]
+    float* vs = qs + RET_TB * rowf;                              // [TB][JT]
+    for (int i = threadIdx.x; i < 2 * RET_TB * rowf; i += RET_THREADS) ks[i] = 0.f;    // slots beyond dim stay zero
+    const float g = decay[h];
+    float S[RET_RMAX];
+    float* sp = state + (((size_t)slot * a.H + h) * a.dim) * a.vd;
+#pragma unroll
+    for (int r = 0; r < RET_RMAX; r++) {
+        const int i = l * per + r;
+        S[r] = (on && r < per && i < a.dim) ? sp[(size_t)i * a.vd + j] : 0.f;
+    }
+    const int n = a.H * a.dim;
+    for (int t0 = q0; t0 < q1; t0 += RET_TB) {
+        const int nt = min(RET_TB, q1 - t0);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * a.dim; idx += RET_THREADS) {
+            const int tt = idx / a.dim, i = idx % a.dim;
+            const size_t src = (size_t)(t0 + tt) * n + (size_t)h * a.dim + i;
+            const int dst = tt * rowf + (i / per) * CS + i % per;
+            ks[dst] = kn[src];
+            qs[dst] = qn[src];
+        }
+        for (int idx = threadIdx.x; idx < nt * JT; idx += RET_THREADS) {
+            const int tt = idx / JT, c = idx % JT;
+            const int col = blockIdx.x * JT + c;
+            vs[idx] = col < a.vd ? to_f32(v[(size_t)(t0 + tt) * a.ldv + a.v_off + (size_t)h * a.vd + col]) : 0.f;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; tt++) {
+            const float* kk = ks + tt * rowf + l * CS;
+            const float* qq = qs + tt * rowf + l * CS;
+            const float vj = vs[tt * JT + jl];
+            float acc = 0.f;
+#pragma unroll
+            for (int r = 0; r < RET_RMAX; r++) {
+                if (r < per) {
+                    S[r] = fmaf(kk[r], vj, g * S[r]);
+                    acc = fmaf(S[r], qq[r], acc);
+                }
+            }
+            for (int m = 1; m < L; m <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+            if (on && l == 0) o[(size_t)(t0 + tt) * a.H * a.vd + (size_t)h * a.vd + j] = acc;
+        }
+    }
+    if (on) {
+#pragma unroll
+        for (int r = 0; r < RET_RMAX; r++) {
+            const int i = l * per + r;
+            if (r < per && i < a.dim) sp[(size_t)i * a.vd + j] = S[r];
+        }
+    }
+}
+
+}  // namespace
+
+// qk: rows that hold every head's q from column q_off and every head's k from column k_off; qn, kn: fp32 [T][H*dim].
+MYNAH_API int mynah_retention_prep(const void* qk, int ld, int q_off, int k_off, int dtype, float* qn, float* kn,
+                                   int T, int H, int dim, const float* cos_t, const float* sin_t, int rot,
+                                   int interleaved, int n_pos, float k_scale, const int* tok_seq, const int* tok_pos,
+                                   int* status, cudaStream_t stream) {
+    if (T == 0) return 0;
+    MYNAH_REQUIRE(T > 0 && H > 0 && dim > 0, "retention_prep: bad sizes");
+    MYNAH_REQUIRE(rot % 2 == 0 && rot <= dim, "retention_prep: %d rotated dims do not fit a head of %d", rot, dim);
+    const RetPrepArgs a{H, dim, ld, q_off, k_off, cos_t ? rot : 0, interleaved, n_pos, k_scale};
+    if (dtype == MYNAH_F32)
+        mynah_launch(retention_prep_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)qk, qn, kn, cos_t, sin_t,
+                     tok_seq, tok_pos, a, status);
+    else if (dtype == MYNAH_BF16)
+        mynah_launch(retention_prep_kernel<bf16>, dim3(T), dim3(128), 0, stream, (const bf16*)qk, qn, kn, cos_t, sin_t,
+                     tok_seq, tok_pos, a, status);
+    else
+        return mynah_fail("retention_prep: unsupported dtype %d", dtype);
+    return mynah_check_launch("retention_prep");
+}
+
+// v: rows whose columns [v_off + h * vd, ...) are head h's values; decay: fp32 [H]; state: fp32 [n_slots + 1][H][dim][vd];
+// o: fp32 [T][H * vd].
+MYNAH_API int mynah_retention_scan(const float* qn, const float* kn, const void* v, int ldv, int v_off, int v_dtype,
+                                   const float* decay, float* state, int n_slots, float* o, const int* cu_q,
+                                   const int* slots, int B, int H, int dim, int vd, cudaStream_t stream) {
+    if (B == 0) return 0;
+    MYNAH_REQUIRE(B > 0 && H > 0 && dim > 0 && vd > 0, "retention_scan: bad sizes");
+    MYNAH_REQUIRE(dim <= 512, "retention_scan: keys of %d values exceed the 512 that the kernel stages", dim);
+    MYNAH_REQUIRE(H <= 65535 && B <= 65535, "retention_scan: too many heads or sequences for one launch");
+    int L = 1;
+    while (L * RET_RMAX < dim) L <<= 1;
+    const int per = ceil_div(dim, L);
+    const int JT = RET_THREADS / L;
+    const RetArgs a{B, H, dim, vd, n_slots, ldv, v_off, L, per};
+    const size_t smem = ((size_t)2 * RET_TB * (per + 1) * L + (size_t)RET_TB * JT) * sizeof(float);
+    const dim3 grid(ceil_div(vd, JT), H, B);
+    if (v_dtype == MYNAH_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(retention_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        mynah_launch(retention_scan_kernel<float>, grid, dim3(RET_THREADS), smem, stream, qn, kn, (const float*)v, decay, state, o, cu_q, slots, a);
+    } else if (v_dtype == MYNAH_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(retention_scan_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        mynah_launch(retention_scan_kernel<bf16>, grid, dim3(RET_THREADS), smem, stream, qn, kn, (const bf16*)v, decay, state, o, cu_q, slots, a);
+    } else
+        return mynah_fail("retention_scan: unsupported dtype %d", v_dtype);
+    return mynah_check_launch("retention_scan");
+}

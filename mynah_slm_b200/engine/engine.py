@@ -221,13 +221,14 @@ class Engine:
         self.spec = spec
         self.dtype = dtype
         self.model = Model(spec)
-        self.runtime = Runtime(self.device, dtype, spec.max_positions)
+        self.n_pages = max(1, -(-int(max_tokens) // PAGE_TOKENS))
+        # no sequence outgrows the cache, so position tables need not reach further than its pages do
+        self.runtime = Runtime(self.device, dtype, min(spec.max_positions, self.n_pages * PAGE_TOKENS))
         from ..weights.random_init import RandomWeights, fill_into
         if isinstance(checkpoint, RandomWeights):
             fill_into(self.model.tensor_specs(), checkpoint, self.runtime)
         else:
             load_into(self.model.tensor_specs(), checkpoint, self.runtime)
-        self.n_pages = max(1, -(-int(max_tokens) // PAGE_TOKENS))
         self.max_seqs = int(max_seqs) if max_seqs else min(self.n_pages, 1024)
         self.cache = Cache(self.model.cache_plan(), self.n_pages, self.max_seqs, dtype, self.device)
         self.n_groups = len(self.cache.plan.groups)

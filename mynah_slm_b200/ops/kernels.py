@@ -44,20 +44,22 @@ class PageTableView:
     n_pages: int
 
 
-def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 scale: float = 1.0) -> torch.Tensor:
+    """x[t] = table[token_t] * scale, fp32 [T, D]."""
     _chk(table, "embedding table", dim=2)
     _chk(tokens, "tokens", torch.int32, 1)
     T, (V, D) = tokens.numel(), table.shape
     if out is None:
         out = torch.empty((T, D), dtype=torch.float32, device=table.device)
-    call("mynah_embed_gather", ptr(table), code(table.dtype), ptr(tokens), ptr(out), T, D, V, stream_ptr())
+    call("mynah_embed_gather", ptr(table), code(table.dtype), ptr(tokens), ptr(out), T, D, V, float(scale), stream_ptr())
     return out
 
 
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, act_dtype: torch.dtype,
             delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
-            out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """h = RMSNorm(x (+ delta)) * gain. Without `rows`, x is updated in place when delta is given; with `rows`
+            out: Optional[torch.Tensor] = None, delta_scale: float = 1.0) -> torch.Tensor:
+    """h = RMSNorm(x (+ delta_scale * delta)) * gain. Without `rows`, x is updated in place when delta is given; with `rows`
     (which may name a row more than once) x is only read."""
     _chk(x, "residual", torch.float32, 2)
     _chk(gain, "norm gain", dim=1)
@@ -75,16 +77,16 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, act_dtype: torch.dt
     if out is None:
         out = torch.empty((n, D), dtype=act_dtype, device=x.device)
     call("mynah_rmsnorm", ptr(x), ptr(delta), ptr(gain), code(gain.dtype), ptr(rows), ptr(out), code(act_dtype),
-         n, D, float(eps), stream_ptr())
+         n, D, float(eps), float(delta_scale), stream_ptr())
     return out
 
 
-def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
+def residual_add(x: torch.Tensor, delta: torch.Tensor, scale: float = 1.0) -> None:
     _chk(x, "residual", torch.float32)
     _chk(delta, "delta")
     if delta.shape != x.shape:
         raise KernelError("residual_add: shapes differ")
-    call("mynah_residual_add", ptr(x), ptr(delta), code(delta.dtype), x.numel(), stream_ptr())
+    call("mynah_residual_add", ptr(x), ptr(delta), code(delta.dtype), x.numel(), float(scale), stream_ptr())
 
 
 def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -103,15 +105,17 @@ class NormedInput:
     the gain. A matrix product that can compute the norm on its way takes it as
     it is (`linear`, `linear_swiglu`); anything else calls `materialize`."""
 
-    def __init__(self, stream, delta, gain: torch.Tensor, eps: float, act_dtype: torch.dtype):
+    def __init__(self, stream, delta, gain: torch.Tensor, eps: float, act_dtype: torch.dtype, delta_scale: float = 1.0):
         self.stream, self.delta, self.gain, self.eps, self.act_dtype = stream, delta, gain, float(eps), act_dtype
+        self.delta_scale = float(delta_scale)
         self.shape = stream.x.shape
         self.dtype = act_dtype
         self._h: Optional[torch.Tensor] = None
 
     def materialize(self) -> torch.Tensor:
         if self._h is None:
-            self._h = rmsnorm(self.stream.x, self.gain, self.eps, self.act_dtype, delta=self.delta)
+            self._h = rmsnorm(self.stream.x, self.gain, self.eps, self.act_dtype, delta=self.delta,
+                              delta_scale=self.delta_scale)
             self.delta = None
         return self._h
 
@@ -139,7 +143,8 @@ def gemv_decode_supported(M: int, N: int, K: int) -> bool:
 def _gemv_decode(x, w: torch.Tensor, N: int, epilogue: int, out: torch.Tensor) -> torch.Tensor:
     """x: bf16 rows [M, K] or a NormedInput. epilogue 0: bf16, 1: SwiGLU (w holds N gate rows then N up rows), 2: fp32."""
     K = w.shape[1]
-    if isinstance(x, NormedInput) and x._h is None and (x.shape[0] > FUSED_NORM_MAX_ROWS or not _norm_prologue_fits(x.shape[0], K)):
+    if isinstance(x, NormedInput) and x._h is None and (x.shape[0] > FUSED_NORM_MAX_ROWS or not _norm_prologue_fits(x.shape[0], K)
+                                                        or (x.delta is not None and x.delta_scale != 1.0)):
         x.materialize()
     if isinstance(x, NormedInput) and x._h is None:
         st = x.stream
@@ -511,7 +516,7 @@ def l2_prefetch(tensors) -> None:
 
 
 # ------------------------------------------------------------------ parts of mixers with recurrent state
-ACTIVATIONS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+ACTIVATIONS = {"gelu": 0, "gelu_erf": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "relu2": 4}
 
 
 def embed_positions(table: torch.Tensor, pos_table: torch.Tensor, tokens: torch.Tensor, tok_pos: torch.Tensor,
@@ -781,3 +786,132 @@ def attn_decode_tc_masked(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: i
     call("mynah_attn_decode_tc_ex", ptr(q), ptr(out), ctx.B, H, KV, HD, q.shape[1], out.shape[1],
          ptr(k_cache), ptr(v_cache), ptr(ctx.kv_len), ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages,
          window or 0, chunk or 0, float(scale), ctx.decode_splits, ptr(scratch), None, ptr(ctx.status), stream_ptr())
+
+
+# ------------------------------------------------------------------ latent attention, retention, routed experts
+def scale_(x: torch.Tensor, s: float) -> torch.Tensor:
+    """x *= s in place (fp32)."""
+    _chk(x, "rows", torch.float32)
+    call("mynah_scale_f32", ptr(x), x.numel(), float(s), stream_ptr())
+    return x
+
+
+def rope_table_freqs(n_pos: int, freqs, mult: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin [n_pos, pairs] of the angles position * freqs[i], each times `mult`; angles in double."""
+    f = torch.as_tensor(freqs, dtype=torch.float64).to(device).contiguous()
+    half = f.numel()
+    cos = torch.empty((n_pos, half), dtype=torch.float32, device=device)
+    sin = torch.empty((n_pos, half), dtype=torch.float32, device=device)
+    call("mynah_rope_table_freqs", ptr(cos), ptr(sin), n_pos, half, ptr(f), float(mult), stream_ptr())
+    return cos, sin
+
+
+def latent_prep(q: torch.Tensor, q_off: int, dkv: Optional[torch.Tensor], dkv_off: int, q_out: torch.Tensor,
+                H: int, dim: int, rd: int, r: int, HDp: int, w: Optional[torch.Tensor], eps: float, cos, sin, rot: int,
+                interleaved: bool, ctx, pages: PageTableView, k_cache: Optional[torch.Tensor]) -> None:
+    """Latent norm, rotation of the shared key part and of every head's rotated query part, cache write
+    (csrc/latent_attn.cu). q_out [T, H * HDp]: columns [r, HDp) of every head are written."""
+    _rows(q, "latent_prep: q")
+    _chk(q_out, "packed queries", q.dtype, 2)
+    if q_out.shape[1] != H * HDp:
+        raise KernelError("latent_prep: the packed query rows do not have heads x stored width columns")
+    if q.shape[1] < q_off + H * (dim + rd):
+        raise KernelError("latent_prep: the query projection's rows are too short")
+    if (dkv is None) != (k_cache is None):
+        raise KernelError("latent_prep: the down-projection and the cache go together")
+    if dkv is not None:
+        _rows(dkv, "latent_prep: down-projection")
+        if dkv.dtype != q.dtype or k_cache.dtype != q.dtype:
+            raise KernelError("latent_prep: activations and cache differ in dtype")
+        if dkv.shape[1] < dkv_off + r + rd:
+            raise KernelError("latent_prep: the down-projection's rows are too short")
+        if tuple(k_cache.shape[1:]) != (1, PAGE_TOKENS, HDp) or not k_cache.is_contiguous():
+            raise KernelError(f"latent_prep: cache pages are {tuple(k_cache.shape[1:])}, expected {(1, PAGE_TOKENS, HDp)}")
+        _chk(w, "latent norm weight", dim=1)
+        if w.numel() != r:
+            raise KernelError("latent_prep: the norm weight does not match the latent")
+    n_pos = cos.shape[0] if cos is not None else 0
+    if cos is not None and cos.shape[1] * 2 != rot:
+        raise KernelError("latent_prep: the rotation table does not match the rotated dims")
+    call("mynah_latent_prep", ptr(q), q.stride(0), q_off, ptr(dkv), dkv.stride(0) if dkv is not None else 0, dkv_off,
+         code(q.dtype), ptr(q_out), q.shape[0], H, dim, rd, r, HDp, ptr(w), code(w.dtype) if w is not None else 0,
+         float(eps), ptr(cos), ptr(sin), rot if cos is not None else 0, 1 if interleaved else 0, n_pos,
+         ptr(ctx.tok_seq), ptr(ctx.tok_pos), ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages,
+         ptr(k_cache), ptr(ctx.status), stream_ptr())
+
+
+def head_linear(x: torch.Tensor, head_in: int, in_off: int, W: torch.Tensor, out: torch.Tensor, head_out: int,
+                out_off: int) -> torch.Tensor:
+    """out[t, h * head_out + out_off + j] = sum_i W[h, j, i] * x[t, h * head_in + in_off + i]: one small product a head
+    (csrc/latent_attn.cu). W [H, n_out, n_in] in the rows' type; fp32 accumulation."""
+    _rows(x, "head_linear: input")
+    _rows(out, "head_linear: output")
+    _chk(W, "head_linear: weights", x.dtype, 3)
+    if out.dtype != x.dtype or out.shape[0] != x.shape[0]:
+        raise KernelError("head_linear: input and output rows differ")
+    H, n_out, n_in = W.shape
+    if (H - 1) * head_in + in_off + n_in > x.shape[1] or (H - 1) * head_out + out_off + n_out > out.shape[1]:
+        raise KernelError("head_linear: the heads do not fit the rows")
+    call("mynah_head_linear", ptr(x), ptr(W), ptr(out), code(x.dtype), x.shape[0], H, n_in, n_out,
+         x.stride(0), head_in, in_off, out.stride(0), head_out, out_off, stream_ptr())
+    return out
+
+
+def retention_prep(p: torch.Tensor, q_off: int, k_off: int, H: int, dim: int, cos, sin, rot: int, interleaved: bool,
+                   k_scale: float, ctx):
+    """fp32 q and k of every head, rotated; k also scaled (csrc/retention.cu). p: the projection's rows."""
+    _rows(p, "retention_prep: projection")
+    if max(q_off, k_off) + H * dim > p.shape[1]:
+        raise KernelError("retention_prep: the projection's rows are too short")
+    T = p.shape[0]
+    qn = torch.empty((T, H * dim), dtype=torch.float32, device=p.device)
+    kn = torch.empty((T, H * dim), dtype=torch.float32, device=p.device)
+    n_pos = cos.shape[0] if cos is not None else 0
+    if cos is not None and cos.shape[1] * 2 != rot:
+        raise KernelError("retention_prep: the rotation table does not match the rotated dims")
+    call("mynah_retention_prep", ptr(p), p.stride(0), q_off, k_off, code(p.dtype), ptr(qn), ptr(kn), T, H, dim,
+         ptr(cos), ptr(sin), rot if cos is not None else 0, 1 if interleaved else 0, n_pos, float(k_scale),
+         ptr(ctx.tok_seq), ptr(ctx.tok_pos), ptr(ctx.status), stream_ptr())
+    return qn, kn
+
+
+def retention_scan(qn: torch.Tensor, kn: torch.Tensor, v: torch.Tensor, v_off: int, decay: torch.Tensor,
+                   state: torch.Tensor, ctx, H: int, dim: int, vd: int) -> torch.Tensor:
+    """The decayed recurrence; state fp32 [max_seqs + 1, H, dim, vd]; returns o fp32 [T, H * vd]."""
+    _rows(v, "retention_scan: v")
+    _chk(state, "retention state", torch.float32, 4)
+    _chk(decay, "decays", torch.float32, 1)
+    if tuple(state.shape[1:]) != (H, dim, vd) or decay.numel() != H:
+        raise KernelError("retention_scan: the state or the decays do not fit")
+    if v_off + H * vd > v.shape[1]:
+        raise KernelError("retention_scan: the value rows are too short")
+    T = v.shape[0]
+    o = torch.empty((T, H * vd), dtype=torch.float32, device=v.device)
+    call("mynah_retention_scan", ptr(qn), ptr(kn), ptr(v), v.stride(0), v_off, code(v.dtype), ptr(decay), ptr(state),
+         state.shape[0] - 1, ptr(o), ptr(ctx.cu_q), ptr(ctx.slots), ctx.B, H, dim, vd, stream_ptr())
+    return o
+
+
+def moe_table_ffn(h: torch.Tensor, table: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ctx, top: int,
+                  limit: float, alpha: float) -> torch.Tensor:
+    """Experts picked per token id from `table` [vocab, top], equal weights (csrc/moe.cu). w_gu [E, 2, F, D],
+    w_down [E, D, F]; returns [T, D] in the rows' type."""
+    _chk(h, "rows", dim=2)
+    _chk(table, "expert table", torch.int32, 2)
+    _chk(w_gu, "gate/up weights", h.dtype, 4)
+    _chk(w_down, "down weights", h.dtype, 3)
+    T, D = h.shape
+    E, _, F, _ = w_gu.shape
+    if tuple(w_gu.shape) != (E, 2, F, D) or tuple(w_down.shape) != (E, D, F) or table.shape[1] != top:
+        raise KernelError("moe_table_ffn: sizes do not fit")
+    P_ = T * top
+    dev = h.device
+    out = torch.empty((T, D), dtype=h.dtype, device=dev)
+    y = torch.empty((P_, F), dtype=h.dtype, device=dev)
+    o = torch.empty((P_, D), dtype=torch.float32, device=dev)
+    ints = torch.empty((2 * P_ + 1 + 3 * int(lib.load().mynah_moe_max_tiles(T, top, E)),), dtype=torch.int32, device=dev)
+    call("mynah_moe_table_ffn", ptr(h), code(h.dtype), ptr(ctx.tokens), ptr(ctx.tok_seq), ptr(table), ptr(w_gu),
+         ptr(w_down), ptr(out), ptr(y), ptr(o), ptr(ints), T, table.shape[0], top, E, D, F, float(limit), float(alpha),
+         1.0 / top, ptr(ctx.status), stream_ptr())
+    lib.add_launches(3)                       # route, two products, combine
+    return out

@@ -26,9 +26,9 @@ _lib: ctypes.CDLL | None = None
 
 P = c_void_p
 _SIGNATURES: dict[str, list] = {
-    "mynah_embed_gather": [P, c_int, P, P, c_int, c_int, c_int, P],
-    "mynah_rmsnorm": [P, P, P, c_int, P, P, c_int, c_int, c_int, c_float, P],
-    "mynah_residual_add": [P, P, c_int, c_longlong, P],
+    "mynah_embed_gather": [P, c_int, P, P, c_int, c_int, c_int, c_float, P],
+    "mynah_rmsnorm": [P, P, P, c_int, P, P, c_int, c_int, c_int, c_float, c_float, P],
+    "mynah_residual_add": [P, P, c_int, c_longlong, c_float, P],
     "mynah_swiglu": [P, P, c_int, c_int, c_int, P],
     "mynah_gemm_f32": [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P],
     "mynah_rope_table": [P, P, c_int, c_int, c_double, P],
@@ -108,6 +108,16 @@ _SIGNATURES: dict[str, list] = {
     "mynah_delta_prep": [P, c_int, P, P, c_int, c_int, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, P],
     "mynah_delta_rule": [P, P, P, c_int, c_int, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
     "mynah_gated_rmsnorm": [P, P, c_int, c_int, P, c_int, P, c_int, c_int, c_int, c_float, P],
+    "mynah_scale_f32": [P, c_longlong, c_float, P],
+    "mynah_rope_table_freqs": [P, P, c_int, c_int, P, c_double, P],
+    "mynah_latent_prep": [P, c_int, c_int, P, c_int, c_int, c_int, P, c_int, c_int, c_int, c_int, c_int, c_int,
+                          P, c_int, c_float, P, P, c_int, c_int, c_int, P, P, P, P, P, c_int, P, P, P],
+    "mynah_head_linear": [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P],
+    "mynah_retention_prep": [P, c_int, c_int, c_int, c_int, P, P, c_int, c_int, c_int, P, P, c_int, c_int, c_int,
+                             c_float, P, P, P, P],
+    "mynah_retention_scan": [P, P, P, c_int, c_int, c_int, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, P],
+    "mynah_moe_table_ffn": [P, c_int, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_float, c_float, c_float, P, P],
 }
 
 
@@ -149,6 +159,8 @@ def load() -> ctypes.CDLL:
     lib.mynah_gemm_tcgen05_splits_k.argtypes = [c_int, c_int, c_int, c_int]
     lib.mynah_gemv_decode_supported.restype = c_int
     lib.mynah_gemv_decode_supported.argtypes = [c_int, c_int, c_int]
+    lib.mynah_moe_max_tiles.restype = c_int
+    lib.mynah_moe_max_tiles.argtypes = [c_int, c_int, c_int]
     for name, args in _SIGNATURES.items():
         try:
             fn = getattr(lib, name)

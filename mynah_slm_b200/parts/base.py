@@ -209,23 +209,32 @@ class Block(Part):
 
 class Residual:
     """The residual stream of a step: fp32 [T, hidden], plus at most one
-    delta that has not been added yet. A norm that follows an add takes both
-    and does the add on its way (one pass over the row instead of two)."""
+    delta that has not been added yet, with the constant it is multiplied by
+    on its way in (1 unless a block scales its sublayers' outputs). A norm
+    that follows an add takes both and does the add on its way (one pass over
+    the row instead of two)."""
 
     def __init__(self, x: torch.Tensor):
         self.x = x
         self.pending: Optional[torch.Tensor] = None
+        self.pending_scale: float = 1.0
 
-    def add(self, delta: torch.Tensor) -> None:
+    def add(self, delta: torch.Tensor, scale: float = 1.0) -> None:
         if self.pending is not None:
             self.flush()
-        self.pending = delta
+        self.pending, self.pending_scale = delta, float(scale)
+
+    def take_pending(self):
+        """(delta, scale) of the add that is still to be done, which the caller now owes; (None, 1.0) if none."""
+        delta, scale = self.pending, self.pending_scale
+        self.pending, self.pending_scale = None, 1.0
+        return delta, scale
 
     def flush(self) -> torch.Tensor:
         if self.pending is not None:
             from ..ops import kernels
-            kernels.residual_add(self.x, self.pending)
-            self.pending = None
+            kernels.residual_add(self.x, self.pending, self.pending_scale)
+            self.pending, self.pending_scale = None, 1.0
         return self.x
 
 

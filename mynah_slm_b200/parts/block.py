@@ -5,6 +5,11 @@ the reference's block (mynah-slm docs/qwen3-arch.md:33-47,
 src/arch_qwen3.c:201-234). It places two norms, named "mixer" and "ffn". Each
 add is left pending on the stream, so the norm that follows does it in the
 same pass.
+
+Two parameters, both optional: `residual_mult` m (default 1) multiplies every
+sublayer's output on its way into the stream, x = x + m * mixer(norm(x)); the
+product is formed in fp32 by the kernel that does the add. A layer may have no
+feed-forward (`ffn` None, and then no "ffn" norm).
 """
 from __future__ import annotations
 
@@ -15,15 +20,18 @@ from .base import Block, CacheView, Residual, register_block
 class PreNormResidual(Block):
     def __init__(self, spec, mixer, ffn, norms):
         super().__init__(spec, mixer, ffn, norms)
-        for need in ("mixer", "ffn"):
+        for need in ("mixer",) + (("ffn",) if ffn is not None else ()):
             if need not in self.norms:
                 raise ConfigError(f"prenorm_residual: the layer gives no {need!r} norm")
+        self.mult = float(spec.get("residual_mult", 1.0))
 
     def forward(self, stream: Residual, ctx, cache: CacheView) -> None:
         h = self.norms["mixer"].apply(stream, lazy=getattr(self.mixer, "accepts_normed", False))
-        stream.add(self.mixer.forward(h, ctx, cache))
+        stream.add(self.mixer.forward(h, ctx, cache), self.mult)
+        if self.ffn is None:
+            return
         h = self.norms["ffn"].apply(stream, lazy=getattr(self.ffn, "accepts_normed", False))
-        stream.add(self.ffn.forward(h, ctx))
+        stream.add(self.ffn.forward(h, ctx), self.mult)
 
 
 register_block("prenorm_residual", PreNormResidual)

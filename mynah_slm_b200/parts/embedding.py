@@ -1,7 +1,9 @@
 """Token embedding and output head.
 
 Embedding: x = E[token], no scaling by sqrt(hidden) (mynah-slm
-src/arch_qwen3.c:186). Head: logits = Head . h in fp32, where Head is the
+src/arch_qwen3.c:186); a design that multiplies its embedding by a constant
+gives `scale` (the product is fp32), and one that multiplies its logits by a
+constant gives the head `logit_scale`. Head: logits = Head . h in fp32, where Head is the
 embedding matrix when the configuration ties them and `lm_head.weight`
 otherwise; the configuration decides, not the presence of the tensor
 (docs/qwen3-arch.md:91-113: the official checkpoint ships a duplicate
@@ -22,6 +24,7 @@ class TokenEmbedding(Embedding):
         super().__init__(spec)
         self.name = str(spec["name"])
         self.V, self.D = int(spec["vocab_size"]), int(spec["dim"])
+        self.scale = float(spec.get("scale", 1.0))
         self.table: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> list[TensorSpec]:
@@ -31,7 +34,7 @@ class TokenEmbedding(Embedding):
         self.table = tensors[self.name]
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
-        return kernels.embed_gather(self.table, tokens)
+        return kernels.embed_gather(self.table, tokens, scale=self.scale)
 
 
 class LinearHead(Head):
@@ -41,6 +44,7 @@ class LinearHead(Head):
         self.name = str(spec["name"])
         self.V, self.D = int(spec["vocab_size"]), int(spec["dim"])
         self.embedding = embedding
+        self.logit_scale = float(spec.get("logit_scale", 1.0))
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> list[TensorSpec]:
@@ -54,7 +58,8 @@ class LinearHead(Head):
         self.weight = self.embedding.table if self.tied else tensors[self.name]
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return kernels.linear(h, self.weight, out_dtype=torch.float32)
+        logits = kernels.linear(h, self.weight, out_dtype=torch.float32)
+        return logits if self.logit_scale == 1.0 else kernels.scale_(logits, self.logit_scale)
 
 
 register_embedding("token_embedding", TokenEmbedding)

@@ -1,9 +1,11 @@
 """Dense feed-forward without a gate: x -> W_down . act(W_up . x), no bias.
 
 Parameters: hidden_size, intermediate_size, activation ("gelu" or "gelu_erf":
-0.5 z (1 + erf(z / sqrt 2)); "gelu_tanh"; "silu"; "relu"), and the two
-tensors' names (`up`, `down`). The activation is computed in fp32 from the
-product's rows.
+0.5 z (1 + erf(z / sqrt 2)); "gelu_tanh"; "silu"; "relu"; "relu2", the square
+of relu), and the two tensors' names (`up`, `down`). The activation is
+computed in fp32 from the product's rows. `output` says in what type the last
+product leaves its rows: "fp32" (the default: unrounded, for a norm that
+follows the sublayer) or "act" (the run's activation type, for a residual add).
 """
 from __future__ import annotations
 
@@ -25,6 +27,7 @@ class DenseMLP(FeedForward):
         if self.act not in kernels.ACTIVATIONS:
             raise ConfigError(f"dense_mlp: activation {self.act!r} is not built in "
                               f"(known: {', '.join(sorted(kernels.ACTIVATIONS))})")
+        self.out_fp32 = str(spec.get("output", "fp32")) == "fp32"
         self.up_name, self.down_name = str(spec["up"]), str(spec["down"])
         self.w_up = self.w_down = None
 
@@ -40,7 +43,7 @@ class DenseMLP(FeedForward):
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
         u = kernels.linear(h, self.w_up)
         kernels.activation(u, self.act, out=u)
-        return kernels.linear(u, self.w_down, out_dtype=torch.float32)     # unrounded into the norm that follows
+        return kernels.linear(u, self.w_down, out_dtype=torch.float32 if self.out_fp32 else None)
 
 
 register_ffn("dense_mlp", DenseMLP)

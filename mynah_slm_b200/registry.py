@@ -86,6 +86,8 @@ def _register_builtin() -> None:
     register_architecture(ARCHITECTURE, Qwen3Config.from_dict, replace=True)
     from .config import supisun
     register_architecture(supisun.ARCHITECTURE, supisun.SupisunConfig.from_dict, replace=True)
+    from .config import nedupel
+    register_architecture(nedupel.ARCHITECTURE, nedupel.NedupelConfig.from_dict, replace=True)
 
 
 _register_builtin()

@@ -50,6 +50,21 @@ def _mean_std(ts: TensorSpec) -> tuple[float, float]:
     raise ValueError(f"{ts.name}: unknown init {ts.init!r}")
 
 
+def table_tensor(ts: TensorSpec, seed: int) -> torch.Tensor:
+    """An integer table of the random model. init "distinct:N": every row holds different numbers below N (a row
+    starts at a number that depends on the row and the seed, and goes on in equal steps); anything else: zeros."""
+    if not ts.init.startswith("distinct:"):
+        return torch.zeros(ts.shape, dtype=torch.int32)
+    n = int(ts.init.split(":", 1)[1])
+    rows, per = ts.shape
+    if per > n:
+        raise ValueError(f"{ts.name}: {per} different numbers below {n} do not exist")
+    start = (np.arange(rows, dtype=np.uint64) * np.uint64(2654435761) + np.uint64(int(seed) & 0xFFFFFFFF)) >> np.uint64(7)
+    step = max(n // per, 1)
+    table = (start[:, None] + np.arange(per, dtype=np.uint64)[None, :] * np.uint64(step)) % np.uint64(n)
+    return torch.from_numpy(table.astype(np.int32))
+
+
 def _wanted(model: Model) -> list[TensorSpec]:
     seen, out = set(), []
     for _, ts in model.tensor_specs():
@@ -64,7 +79,7 @@ def host_tensor(ts: TensorSpec, seed: int, dtype: torch.dtype) -> torch.Tensor:
     """One tensor of the random model, made by the native host runtime."""
     from ..cache.pages import host_library
     if ts.role == "table":
-        return torch.zeros(ts.shape, dtype=torch.int32)
+        return table_tensor(ts, seed)
     if dtype not in (torch.float32, torch.bfloat16):
         raise ValueError(f"random weights are written as float32 or bfloat16, not {dtype}")
     n = int(np.prod(ts.shape)) if len(ts.shape) else 1
@@ -101,7 +116,7 @@ def device_tensor(ts: TensorSpec, seed: int, dtype: torch.dtype, device) -> torc
     """One tensor of the random model, made on the device by `mynah_randn_fill`."""
     from ..ops.lib import call, code, ptr, stream_ptr
     if ts.role == "table":
-        return torch.zeros(ts.shape, dtype=torch.int32, device=device)
+        return table_tensor(ts, seed).to(device)
     t = torch.empty(ts.shape, dtype=dtype, device=device)
     mean, std = _mean_std(ts)
     call("mynah_randn_fill", ptr(t), code(dtype), t.numel(), int(seed) & MASK64, tensor_key(ts.name), mean, std, stream_ptr())
