@@ -6,6 +6,7 @@ and 64.
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --workload 4b|8b      (the two larger workloads, a JSON line of their own each)
     python bench.py --design supisun      (the Supisun design beside Qwen3 at equal size, a JSON line of its own)
+    python bench.py --design nedupel      (the Nedupel design beside Supisun and Qwen3 at equal size, likewise)
 
 One JSON line on stdout. A step is one decode step of the batch.
   value     decoded tokens per second, timed on the device with CUDA events
@@ -311,9 +312,35 @@ def supisun_config(shape: str, layers: int) -> dict:
             "canon": {"taps": 3}, "layers": [pattern[i % 4] for i in range(layers)]}
 
 
+# The Nedupel design at layer sizes that resemble a real model's, beside Supisun (the closest existing design: a hybrid of
+# attention and recurrent layers) and Qwen3 at equal width, depth, feed-forward width, heads and vocabulary. Its layers
+# repeat (retention, latent attention, retention, latent attention that reads the cache of the one two layers before);
+# a cache row holds a latent of 96 and a rotated part of 32 values; feed-forwards alternate between dense and 16 experts of
+# half the dense width of which a token uses 2.
+def nedupel_config(shape: str, layers: int) -> dict:
+    c = dict(QWEN3_0_6B)
+    c.update(SHAPES[shape])
+    D, H, HD, F = c["hidden_size"], c["num_attention_heads"], c["head_dim"], c["intermediate_size"]
+    dense = {"kind": "dense", "ff": F}
+    moe = {"kind": "moe", "expert": {"ff": F // 2, "limit": 7.0}, "router": {"experts": 16, "top": 2}}
+    rot = {"dims": 32, "base": 1e6, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}
+    ret = {"type": "retention", "mixer": {"heads": H, "dim": HD, "vdim": HD, "rot": {"dims": HD, "base": 1e6},
+                                          "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(H - 1, 1)) for h in range(H)]}}
+    lat = {"heads": H, "dim": HD - 32, "rot_dim": 32, "vdim": HD, "kv_rank": 96, "scale": HD ** -0.5, "rot": rot}
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            L = dict(ret)
+        else:
+            L = {"type": "latent_attention", "mixer": dict(lat, **({"kv_from": i - 2} if i % 4 == 3 else {}))}
+        out.append(dict(L, mlp=moe if i % 2 else dense))
+    return {"architecture": "Nedupel", "vocab": c["vocab_size"], "width": D, "embedding": {"scale": D ** 0.5},
+            "residual_mult": 0.7, "logit_scale": 0.25, "norm": {"eps": 1e-6}, "layers": out}
+
+
 def run_design(args) -> int:
-    """`--design supisun`: prefill of one 2,048-token prompt and decode steps at --batch behind 2,048-token prompts, for
-    the design and for Qwen3 at equal size (`--model` runs one of the two: for a launch list of that model alone)."""
+    """`--design NAME`: prefill of one 2,048-token prompt and decode steps at --batch behind 2,048-token prompts, for
+    the design and for the existing models at equal size (`--model` runs one of them: for a launch list of that model alone)."""
     import numpy as np
     import torch
 
@@ -332,7 +359,10 @@ def run_design(args) -> int:
         layers = args.layers or q["num_hidden_layers"]
         q["num_hidden_layers"] = layers
         res = {"layers": layers}
-        for name, cfg in (("supisun", supisun_config(shape, layers)), ("qwen3", q)):
+        arms = [("supisun", supisun_config(shape, layers)), ("qwen3", q)]
+        if args.design == "nedupel":
+            arms.insert(0, ("nedupel", nedupel_config(shape, layers)))
+        for name, cfg in arms:
             if args.model and args.model != name:
                 continue
             V = cfg.get("vocab", cfg.get("vocab_size"))
@@ -439,9 +469,9 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of the decode phases")
     ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes, for --only runs (the full line is always 0.6b)")
     ap.add_argument("--workload", default="", choices=["", "4b", "8b"], help="run one of the two larger workloads instead")
-    ap.add_argument("--design", default="", choices=["", "supisun"],
+    ap.add_argument("--design", default="", choices=["", "supisun", "nedupel"],
                     help="measure this design beside Qwen3 at equal size instead (prefill and decode; a line of its own)")
-    ap.add_argument("--model", default="", choices=["", "supisun", "qwen3"], help="with --design: only this one of the two")
+    ap.add_argument("--model", default="", choices=["", "supisun", "nedupel", "qwen3"], help="with --design: only this one of the models")
     args = ap.parse_args()
 
     if args.impl == "reference":

@@ -763,12 +763,15 @@ def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, H: int, 
 def attn_prefill_tcgen05_masked(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int,
                                 k_cache: torch.Tensor, v_cache: torch.Tensor, pages: PageTableView,
                                 window: int, chunk: int, scale: float) -> None:
-    """The tcgen05 prompt attention with a chunk mask beside the window and a given score scale (> 0)."""
-    _chk(q, "q", torch.bfloat16, 2)
-    _chk(out, "attention output", torch.bfloat16, 2)
+    """The tcgen05 prompt attention with a chunk mask beside the window and a given score scale (> 0). q and out may be
+    column slices (some of the heads) of wider rows whose stride is a multiple of 8."""
+    for t, n in ((q, "q"), (out, "attention output")):
+        _rows(t, "attn_prefill_tcgen05: " + n)
+        if t.dtype != torch.bfloat16 or t.stride(0) % 8 or t.data_ptr() % 16:
+            raise KernelError(f"attn_prefill_tcgen05: {n} must be bfloat16 rows, 16-byte aligned")
     _chk(k_cache, "K cache", torch.bfloat16)
     _chk(v_cache, "V cache", torch.bfloat16)
-    call("mynah_attn_prefill_tcgen05_ex", ptr(q), ptr(out), q.shape[0], ctx.B, ctx.max_q_len, H, KV, HD, q.shape[1], out.shape[1],
+    call("mynah_attn_prefill_tcgen05_ex", ptr(q), ptr(out), q.shape[0], ctx.B, ctx.max_q_len, H, KV, HD, q.stride(0), out.stride(0),
          ptr(k_cache), ptr(v_cache), ptr(ctx.cu_q), ptr(ctx.kv_len), ptr(pages.indptr), ptr(pages.ids), ptr(pages.base),
          pages.n_pages, window or 0, chunk or 0, float(scale), ptr(ctx.status), stream_ptr())
 
@@ -776,14 +779,17 @@ def attn_prefill_tcgen05_masked(q: torch.Tensor, out: torch.Tensor, ctx, H: int,
 def attn_decode_tc_masked(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int,
                           k_cache: torch.Tensor, v_cache: torch.Tensor, pages: PageTableView,
                           window: int, chunk: int, scale: float, scratch: torch.Tensor) -> None:
-    """The tensor-core decode attention with a chunk mask instead of the window and a given score scale."""
-    _chk(q, "q", torch.bfloat16, 2)
-    _chk(out, "attention output", torch.bfloat16, 2)
+    """The tensor-core decode attention with a chunk mask instead of the window and a given score scale. q and out may
+    be column slices (some of the heads) of wider rows whose stride is a multiple of 8."""
+    for t, n in ((q, "q"), (out, "attention output")):
+        _rows(t, "attn_decode_tc: " + n)
+        if t.dtype != torch.bfloat16 or t.stride(0) % 8 or t.data_ptr() % 16:
+            raise KernelError(f"attn_decode_tc: {n} must be bfloat16 rows, 16-byte aligned")
     _chk(scratch, "scratch", torch.float32)
     need = ctx.B * H * ctx.decode_splits * (HD + 2)
     if scratch.numel() < need:
         raise KernelError(f"attn_decode_tc: scratch holds {scratch.numel()} floats, {need} are needed")
-    call("mynah_attn_decode_tc_ex", ptr(q), ptr(out), ctx.B, H, KV, HD, q.shape[1], out.shape[1],
+    call("mynah_attn_decode_tc_ex", ptr(q), ptr(out), ctx.B, H, KV, HD, q.stride(0), out.stride(0),
          ptr(k_cache), ptr(v_cache), ptr(ctx.kv_len), ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages,
          window or 0, chunk or 0, float(scale), ctx.decode_splits, ptr(scratch), None, ptr(ctx.status), stream_ptr())
 

@@ -120,8 +120,15 @@ class LatentAttention(Mixer):
         kernels.head_linear(p, self.dim + self.rd, 0, self.w_ukT, q, HDp, 0)
         lat = torch.empty((T, H * HDp), dtype=p.dtype, device=p.device)
         if ctx.is_decode:
-            attention_dispatch.decode_masked(q, lat, ctx, H, 1, HDp, HDp, cache.k, cache.k, pages, self.window or 0, 0,
-                                             self.scale, self.runtime.attn_scratch(ctx.B, H, HDp, ctx.decode_splits))
+            scratch = self.runtime.attn_scratch(ctx.B, H, HDp, ctx.decode_splits)
+            # the tensor-core decode kernel takes up to 16 query heads a kv head: more heads go in groups of 16
+            G = 16 if (H > 16 and attention_dispatch.USE_TC_MASKED and kernels.attn_decode_tc_supported(p.dtype, 16, 1, HDp)
+                       and attention_dispatch._tc_fits(16, 1, ctx.decode_splits)) else H
+            for h0 in range(0, H, G):
+                n = min(G, H - h0)
+                cols = slice(h0 * HDp, (h0 + n) * HDp)
+                attention_dispatch.decode_masked(q[:, cols] if n < H else q, lat[:, cols] if n < H else lat, ctx, n, 1, HDp,
+                                                 HDp, cache.k, cache.k, pages, self.window or 0, 0, self.scale, scratch)
         else:
             attention_dispatch.prefill_masked(q, lat, ctx, H, 1, HDp, HDp, cache.k, cache.k, pages, self.window or 0, 0,
                                               self.scale)

@@ -77,6 +77,7 @@ WIDE = config(128, 200, [
     moe(latent(16, 16, 32, 8, 96, 0.2, base=500.0, scaling=(2.0, 128, 32.0, 1.0)), 64, 2.0, 8, 2),
     bare(latent(2, 64, 16, 64, 48, 0.1, base=10000.0, kv_from=0)),
     bare(retention(2, 128, 64, [0.99, 0.9], rot=(128, 10000.0))),
+    bare(latent(20, 8, 16, 8, 48, 0.3, base=700.0)),              # more than 16 heads: decode steps take them in groups
 ])
 # the large ends: a cache row of 256 values, keys of 256 and 300 in retention, many experts, a wide expert
 LARGE = config(96, 180, [
