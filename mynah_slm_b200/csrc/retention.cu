@@ -3,7 +3,7 @@
 //
 //   S_t = decay_h S_(t-1) + k_t v_t^T,      o_t = S_t^T q_t
 //
-// Two kernels (the per-head unit RMS and the gate that follow are `gated_rmsnorm`):
+// Kernels (the per-head unit RMS and the gate that follow are `gated_rmsnorm`):
 //
 //   retention_prep   q, k rows -> fp32, the first `rot` dims of every head rotated by the position's table row
 //                    (pairs (i, i + rot/2), or (2i, 2i+1)), k then multiplied by k_scale
@@ -11,6 +11,7 @@
 //                    head of one sequence; a column's dim values lie in the registers of L adjacent lanes (up to
 //                    32 values a lane), which add their parts of o by shuffles in a fixed order. Keys, queries and
 //                    values of 32 tokens at a time pass through shared memory.
+//   retention_chunk  the same recurrence for prompts, a chunk of tokens at a time (see below)
 //
 // All arithmetic is fp32. A sequence's rows are walked in order, so a prompt run whole, in pieces or token by
 // token performs the same operations in the same order.
@@ -148,7 +149,194 @@ retention_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn
     }
 }
 
+// ---- the recurrence chunk by chunk, for prompts ----
+// With a chunk of C tokens, S the state before it and g the head's decay:
+//
+//   o_t   = sum_{s <= t} g^(t-s) (q_t . k_s) v_s  +  g^(t+1) S^T q_t                      t, s inside the chunk
+//   S_new = g^n S + sum_s g^(n-1-s) k_s v_s^T                                            n tokens in the chunk
+//
+// so the 2n dependent steps of a chunk become four blocks of independent multiply-adds: the chunk's score matrix, its
+// product with the values, the read of the old state, and the state's update. A CTA takes 32 columns of one head of one
+// sequence and walks the sequence's chunks in order; q and k of the chunk, the decayed scores, the values and the
+// state's columns lie in shared memory, every product is register-tiled fp32. The powers of g come from a table made
+// by repeated multiplication. Sums run in another order than token by token: the two forms agree to rounding.
+constexpr int RC_THREADS = 256;
+constexpr int RC_JW = 32;                  // columns a CTA
+
+struct RetChunkArgs {
+    int H, dim, vd, n_slots, ldv, v_off;
+};
+
+template <typename T, int C>
+__global__ void __launch_bounds__(RC_THREADS)
+retention_chunk_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const T* __restrict__ v,
+                       const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ o,
+                       const int* __restrict__ cu_q, const int* __restrict__ slots, RetChunkArgs a) {
+    constexpr int TT = C / 16;             // score entries a thread, each way
+    constexpr int TPW = C / 8;             // tokens a warp in the two products with the values and the state
+    extern __shared__ __align__(16) float sm[];
+    griddep_wait();
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int slot = slots[b];
+    const int q0 = cu_q[b], q1 = cu_q[b + 1];
+    if (slot < 0 || slot >= a.n_slots || q1 <= q0) return;
+    const int d = a.dim, ldr = d + 4;      // row stride of q and k in shared memory (16 bytes of padding)
+    const int rpw = d / 8;                 // state rows a warp owns (d is a multiple of 32)
+    float* qs = sm;                        // [C][ldr]
+    float* ks = qs + C * ldr;              // [C][ldr]
+    float* Ss = ks + C * ldr;              // [d][32]
+    float* Ws = Ss + d * RC_JW;            // [C][C + 1]
+    float* vs = Ws + C * (C + 1);          // [C][32]
+    float* gp = vs + C * RC_JW;            // [C + 1]: powers of the decay
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int j = blockIdx.x * RC_JW + lane;
+    const bool on = j < a.vd;
+    const float g = decay[h];
+    if (tid == 0) {
+        float p = 1.f;
+        for (int n = 0; n <= C; n++) {
+            gp[n] = p;
+            p *= g;
+        }
+    }
+    float* sp = state + (((size_t)slot * a.H + h) * d) * a.vd;
+    for (int idx = tid; idx < d * RC_JW; idx += RC_THREADS) {
+        const int i = idx / RC_JW, c = blockIdx.x * RC_JW + idx % RC_JW;
+        Ss[idx] = c < a.vd ? sp[(size_t)i * a.vd + c] : 0.f;
+    }
+    const size_t n = (size_t)a.H * d;
+    for (int t0 = q0; t0 < q1; t0 += C) {
+        const int nt = min(C, q1 - t0);
+        __syncthreads();                                         // the chunk before is done with q, k, v (and gp, S are written)
+        for (int idx = tid; idx < C * (d / 4); idx += RC_THREADS) {
+            const int tt = idx / (d / 4), i4 = (idx % (d / 4)) * 4;
+            float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv;
+            if (tt < nt) {
+                const size_t src = (size_t)(t0 + tt) * n + (size_t)h * d + i4;
+                qv = *reinterpret_cast<const float4*>(qn + src);
+                kv = *reinterpret_cast<const float4*>(kn + src);
+            }
+            *reinterpret_cast<float4*>(qs + tt * ldr + i4) = qv;
+            *reinterpret_cast<float4*>(ks + tt * ldr + i4) = kv;
+        }
+        for (int idx = tid; idx < C * RC_JW; idx += RC_THREADS) {
+            const int tt = idx / RC_JW, c = blockIdx.x * RC_JW + idx % RC_JW;
+            vs[idx] = (tt < nt && c < a.vd) ? to_f32(v[(size_t)(t0 + tt) * a.ldv + a.v_off + (size_t)h * a.vd + c]) : 0.f;
+        }
+        __syncthreads();
+        {   // scores: thread (ta, sb) takes tokens ta + 16 u and keys sb + 16 w
+            const int ta = tid >> 4, sb = tid & 15;
+            float acc[TT][TT];
+#pragma unroll
+            for (int u = 0; u < TT; u++)
+#pragma unroll
+                for (int w = 0; w < TT; w++) acc[u][w] = 0.f;
+            for (int i = 0; i < d; i += 4) {
+                float4 qv[TT], kv[TT];
+#pragma unroll
+                for (int u = 0; u < TT; u++) qv[u] = *reinterpret_cast<const float4*>(qs + (ta + 16 * u) * ldr + i);
+#pragma unroll
+                for (int w = 0; w < TT; w++) kv[w] = *reinterpret_cast<const float4*>(ks + (sb + 16 * w) * ldr + i);
+#pragma unroll
+                for (int u = 0; u < TT; u++)
+#pragma unroll
+                    for (int w = 0; w < TT; w++) {
+                        acc[u][w] = fmaf(qv[u].x, kv[w].x, acc[u][w]);
+                        acc[u][w] = fmaf(qv[u].y, kv[w].y, acc[u][w]);
+                        acc[u][w] = fmaf(qv[u].z, kv[w].z, acc[u][w]);
+                        acc[u][w] = fmaf(qv[u].w, kv[w].w, acc[u][w]);
+                    }
+            }
+#pragma unroll
+            for (int u = 0; u < TT; u++)
+#pragma unroll
+                for (int w = 0; w < TT; w++) {
+                    const int t = ta + 16 * u, s = sb + 16 * w;
+                    Ws[t * (C + 1) + s] = s <= t ? gp[t - s] * acc[u][w] : 0.f;
+                }
+        }
+        __syncthreads();
+        {   // o: warp `warp` takes tokens warp * TPW + u, lane the column
+            float intra[TPW], inter[TPW];
+#pragma unroll
+            for (int u = 0; u < TPW; u++) intra[u] = inter[u] = 0.f;
+            const int tb = warp * TPW;
+            const int s_end = min(tb + TPW, nt);                 // keys beyond the warp's last token weigh nothing
+            for (int s = 0; s < s_end; s++) {
+                const float vv = vs[s * RC_JW + lane];
+#pragma unroll
+                for (int u = 0; u < TPW; u++) intra[u] = fmaf(Ws[(tb + u) * (C + 1) + s], vv, intra[u]);
+            }
+            for (int i = 0; i < d; i += 4) {
+                const float s0 = Ss[i * RC_JW + lane], s1 = Ss[(i + 1) * RC_JW + lane];
+                const float s2 = Ss[(i + 2) * RC_JW + lane], s3 = Ss[(i + 3) * RC_JW + lane];
+#pragma unroll
+                for (int u = 0; u < TPW; u++) {
+                    const float4 qv = *reinterpret_cast<const float4*>(qs + (tb + u) * ldr + i);
+                    inter[u] = fmaf(qv.x, s0, inter[u]);
+                    inter[u] = fmaf(qv.y, s1, inter[u]);
+                    inter[u] = fmaf(qv.z, s2, inter[u]);
+                    inter[u] = fmaf(qv.w, s3, inter[u]);
+                }
+            }
+            if (on) {
+#pragma unroll
+                for (int u = 0; u < TPW; u++) {
+                    const int t = tb + u;
+                    if (t < nt) o[(size_t)(t0 + t) * a.H * a.vd + (size_t)h * a.vd + j] = fmaf(gp[t + 1], inter[u], intra[u]);
+                }
+            }
+        }
+        __syncthreads();                                         // every warp has read the old state
+        {   // the state's rows warp * rpw + r, column `lane`
+            const float gn = gp[nt];
+            for (int r0 = 0; r0 < rpw; r0 += 4) {
+                const int i = warp * rpw + r0;
+                float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+                for (int s = 0; s < nt; s++) {
+                    const float vw = gp[nt - 1 - s] * vs[s * RC_JW + lane];
+                    const float4 kv = *reinterpret_cast<const float4*>(ks + s * ldr + i);
+                    l0 = fmaf(kv.x, vw, l0);
+                    l1 = fmaf(kv.y, vw, l1);
+                    l2 = fmaf(kv.z, vw, l2);
+                    l3 = fmaf(kv.w, vw, l3);
+                }
+                Ss[i * RC_JW + lane] = fmaf(gn, Ss[i * RC_JW + lane], l0);
+                Ss[(i + 1) * RC_JW + lane] = fmaf(gn, Ss[(i + 1) * RC_JW + lane], l1);
+                Ss[(i + 2) * RC_JW + lane] = fmaf(gn, Ss[(i + 2) * RC_JW + lane], l2);
+                Ss[(i + 3) * RC_JW + lane] = fmaf(gn, Ss[(i + 3) * RC_JW + lane], l3);
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < d * RC_JW; idx += RC_THREADS) {
+        const int i = idx / RC_JW, c = blockIdx.x * RC_JW + idx % RC_JW;
+        if (c < a.vd) sp[(size_t)i * a.vd + c] = Ss[idx];
+    }
+}
+
+template <typename T, int C>
+int launch_chunked(const float* qn, const float* kn, const void* v, const float* decay, float* state, float* o,
+                   const int* cu_q, const int* slots, int B, const RetChunkArgs& a, cudaStream_t stream) {
+    const int d = a.dim;
+    const size_t smem = ((size_t)2 * C * (d + 4) + (size_t)d * RC_JW + (size_t)C * (C + 1) + (size_t)C * RC_JW + C + 1 + 3) * sizeof(float);
+    if (cudaFuncSetAttribute(retention_chunk_kernel<T, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return mynah_fail("retention_scan: %zu bytes of shared memory are not to be had", smem);
+    mynah_launch(retention_chunk_kernel<T, C>, dim3(ceil_div(a.vd, RC_JW), a.H, B), dim3(RC_THREADS), smem, stream,
+                 qn, kn, (const T*)v, decay, state, o, cu_q, slots, a);
+    return mynah_check_launch("retention_scan (chunked)");
+}
+
 }  // namespace
+
+// 0: every step walks token by token; otherwise prompts whose longest piece has at least this many tokens go chunk by chunk.
+static int g_ret_chunk_min = 16;
+MYNAH_API int mynah_retention_chunk_min(int n) {
+    const int before = g_ret_chunk_min;
+    g_ret_chunk_min = n;
+    return before;
+}
+
 
 // qk: rows that hold every head's q from column q_off and every head's k from column k_off; qn, kn: fp32 [T][H*dim].
 MYNAH_API int mynah_retention_prep(const void* qk, int ld, int q_off, int k_off, int dtype, float* qn, float* kn,
@@ -171,14 +359,24 @@ MYNAH_API int mynah_retention_prep(const void* qk, int ld, int q_off, int k_off,
 }
 
 // v: rows whose columns [v_off + h * vd, ...) are head h's values; decay: fp32 [H]; state: fp32 [n_slots + 1][H][dim][vd];
-// o: fp32 [T][H * vd].
+// o: fp32 [T][H * vd]. max_q_len: the most tokens a sequence brings (chooses between the two forms of the recurrence).
 MYNAH_API int mynah_retention_scan(const float* qn, const float* kn, const void* v, int ldv, int v_off, int v_dtype,
                                    const float* decay, float* state, int n_slots, float* o, const int* cu_q,
-                                   const int* slots, int B, int H, int dim, int vd, cudaStream_t stream) {
+                                   const int* slots, int B, int H, int dim, int vd, int max_q_len, cudaStream_t stream) {
     if (B == 0) return 0;
     MYNAH_REQUIRE(B > 0 && H > 0 && dim > 0 && vd > 0, "retention_scan: bad sizes");
     MYNAH_REQUIRE(dim <= 512, "retention_scan: keys of %d values exceed the 512 that the kernel stages", dim);
     MYNAH_REQUIRE(H <= 65535 && B <= 65535, "retention_scan: too many heads or sequences for one launch");
+    MYNAH_REQUIRE(v_dtype == MYNAH_F32 || v_dtype == MYNAH_BF16, "retention_scan: unsupported dtype %d", v_dtype);
+    if (g_ret_chunk_min > 0 && max_q_len >= g_ret_chunk_min && dim % 32 == 0 && dim <= 256 &&
+        (((uintptr_t)qn | (uintptr_t)kn) & 15) == 0) {
+        const RetChunkArgs ca{H, dim, vd, n_slots, ldv, v_off};
+        if (v_dtype == MYNAH_F32)
+            return dim <= 128 ? launch_chunked<float, 64>(qn, kn, v, decay, state, o, cu_q, slots, B, ca, stream)
+                              : launch_chunked<float, 32>(qn, kn, v, decay, state, o, cu_q, slots, B, ca, stream);
+        return dim <= 128 ? launch_chunked<bf16, 64>(qn, kn, v, decay, state, o, cu_q, slots, B, ca, stream)
+                          : launch_chunked<bf16, 32>(qn, kn, v, decay, state, o, cu_q, slots, B, ca, stream);
+    }
     int L = 1;
     while (L * RET_RMAX < dim) L <<= 1;
     const int per = ceil_div(dim, L);

@@ -894,8 +894,21 @@ def retention_scan(qn: torch.Tensor, kn: torch.Tensor, v: torch.Tensor, v_off: i
     T = v.shape[0]
     o = torch.empty((T, H * vd), dtype=torch.float32, device=v.device)
     call("mynah_retention_scan", ptr(qn), ptr(kn), ptr(v), v.stride(0), v_off, code(v.dtype), ptr(decay), ptr(state),
-         state.shape[0] - 1, ptr(o), ptr(ctx.cu_q), ptr(ctx.slots), ctx.B, H, dim, vd, stream_ptr())
+         state.shape[0] - 1, ptr(o), ptr(ctx.cu_q), ptr(ctx.slots), ctx.B, H, dim, vd, int(ctx.max_q_len), stream_ptr())
     return o
+
+
+def retention_chunk_min(n: int) -> int:
+    """From how many tokens in a step's longest piece the retention recurrence runs chunk by chunk (keys that are a
+    multiple of 32 values up to 256); 0: always token by token. Returns the setting before. The two forms agree to
+    rounding."""
+    return int(lib.load().mynah_retention_chunk_min(int(n)))
+
+
+def moe_plain(on: bool) -> bool:
+    """Run the experts' bfloat16 products on the plain tiled kernels instead of the tensor-core ones (the tests compare
+    the two). Returns the setting before."""
+    return bool(lib.load().mynah_moe_plain(1 if on else 0))
 
 
 def moe_table_ffn(h: torch.Tensor, table: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ctx, top: int,

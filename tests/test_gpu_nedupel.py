@@ -325,6 +325,35 @@ def test_without_graphs_equals_with(models):
     assert_close(a, b, 1e-6, "captured steps against launched ones")
 
 
+def test_retention_chunk_by_chunk_equals_token_by_token(models):
+    """Prompts through the chunked form of the retention recurrence against the same prompts token by token inside the
+    kernel, alone and in an unequal batch, and the token after (the state the prompts left)."""
+    from mynah_slm_b200.ops import kernels
+    _, cfg, W = models["wide"]
+    seqs = [tokens_for(cfg, n, 500 + n) for n in (300, 129, 5, 191)]
+    runs = []
+    for chunk_min in (16, 0):
+        before = kernels.retention_chunk_min(chunk_min)
+        try:
+            eng = engine(models, "wide", "float32", use_graphs=False)
+            slots = [eng.open_sequence() for _ in seqs]
+            out = eng.step([entry(sl, s, range(len(s))) for sl, s in zip(slots, seqs)]).cpu().numpy()
+            nxt = eng.step([entry(sl, [7], (0,)) for sl in slots]).cpu().numpy()
+            for sl in slots:
+                eng.close_sequence(sl)
+            runs.append((out, nxt))
+        finally:
+            kernels.retention_chunk_min(before)
+    assert_close(runs[1][0], runs[0][0], 2e-5, "chunk by chunk against token by token")
+    assert_close(runs[1][1], runs[0][1], 2e-5, "the token after")
+    at = 0
+    for i, s in enumerate(seqs):
+        ref = plain.forward(cfg, W, s + [7])
+        close(ref[:-1], runs[0][0][at:at + len(s)], "float32", f"batched prompt of {len(s)}")
+        close(ref[-1:], runs[0][1][i:i + 1], "float32", f"the token after the prompt of {len(s)}")
+        at += len(s)
+
+
 def test_random_weights_on_the_device_equal_a_written_folder(tmp_path):
     """`Engine.random` (weights and expert tables made in place) against the folder `write_random_model` writes."""
     import torch

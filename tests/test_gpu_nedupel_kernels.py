@@ -122,7 +122,8 @@ def plain_retention_core(q, k, v, decay, S0=None):
     return o, S
 
 
-@pytest.mark.parametrize("H,dim,vd,rot", [(3, 16, 24, 16), (1, 33, 5, 6), (2, 128, 64, 0), (2, 300, 12, 64)])
+@pytest.mark.parametrize("H,dim,vd,rot", [(3, 16, 24, 16), (1, 33, 5, 6), (2, 128, 64, 0), (2, 300, 12, 64), (2, 256, 40, 64),
+                                          (4, 32, 70, 32), (2, 64, 32, 64)])
 def test_retention_prep_and_scan(H, dim, vd, rot):
     from mynah_slm_b200.ops import kernels
     from mynah_slm_b200.parts.position import rotary_frequencies
@@ -163,6 +164,20 @@ def test_retention_prep_and_scan(H, dim, vd, rot):
         assert rel(ref[s][0].reshape(len(raw[s][0]), -1), np.concatenate(got[s])) < 2e-5
         assert rel(ref[s][1], state[slot].cpu().numpy()) < 2e-5
     assert float(state[2].min()) == 5.0 and float(state[2].max()) == 5.0 and float(state[0].abs().max()) == 0.0
+    # the two forms of the recurrence (chunk by chunk, token by token) on one long piece from a non-zero state
+    q, k, v = raw["a"]
+    p = t32(np.concatenate([x.reshape(na, -1) for x in (q, k, v)], 1))
+    ctx = ctx_for([na], [3])
+    qn, kn = kernels.retention_prep(p, 0, H * dim, H, dim, cos, sin, rot, False, dim ** -0.5, ctx)
+    outs = []
+    for chunk_min in (16, 0):
+        before = kernels.retention_chunk_min(chunk_min)
+        try:
+            st = state.clone()
+            outs.append((kernels.retention_scan(qn, kn, p, 2 * H * dim, t32(decay), st, ctx, H, dim, vd).cpu().numpy(), st[3].cpu().numpy()))
+        finally:
+            kernels.retention_chunk_min(before)
+    assert rel(outs[1][0], outs[0][0]) < 2e-5 and rel(outs[1][1], outs[0][1]) < 2e-5
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -188,6 +203,17 @@ def test_table_routed_experts(dtype, T, D, F, E, top):
     out = kernels.moe_table_ffn(hp, i32(table), w_gu, w_down, ctx, top, limit, 1.702).float().cpu().numpy()
     assert int(ctx.status.item()) == 0
     assert rel(ref, out[:T]) < (2e-5 if dtype == torch.float32 else 3e-2) and np.all(out[T:] == 0)
+    if dtype == torch.bfloat16:
+        # the tensor-core products against the plain tiled ones, and a row's bits in a small step against a large one
+        before = kernels.moe_plain(True)
+        try:
+            plain_out = kernels.moe_table_ffn(hp, i32(table), w_gu, w_down, ctx, top, limit, 1.702).float().cpu().numpy()
+        finally:
+            kernels.moe_plain(before)
+        assert rel(plain_out[:T], out[:T]) < 2e-2
+        few = ctx_for([2], [0], tokens=list(toks[:2]))
+        small = kernels.moe_table_ffn(hp[:2].contiguous(), i32(table), w_gu, w_down, few, top, limit, 1.702).float().cpu().numpy()
+        assert np.array_equal(small, out[:2])
     # an expert id outside the table's range is reported and skipped
     bad = table.copy()
     bad[toks[0], 0] = E
