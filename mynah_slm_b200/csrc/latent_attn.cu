@@ -14,8 +14,10 @@
 //                      both written to the token's cache row; every head's q_r rotated into the packed query rows.
 //                      Pairs are (2i, 2i+1) ("interleaved") or (i, i + dims/2). Norm and rotation in fp32.
 //   head_linear        out[t, h, :] = W_h in[t, h, :] for every head: q_u -> q_a, and latent output -> values
+//                      (bfloat16 on tensor cores, the 32-bit run on fused multiply-adds)
 #include "layout.cuh"
 #include "tile_mm.cuh"
+#include "tile_mma.cuh"
 
 namespace {
 
@@ -154,7 +156,58 @@ head_linear_kernel(const T* __restrict__ in, const T* __restrict__ W, T* __restr
     }
 }
 
+// The same on tensor cores for bfloat16 rows that can move 16 bytes at a time. grid (token tiles of 16 MT, heads,
+// ceil(n_out / (8 warps * 16 columns))).
+template <int MT>
+__global__ void __launch_bounds__(256)
+head_linear_mma_kernel(const bf16* __restrict__ in, const bf16* __restrict__ W, bf16* __restrict__ out, HeadLinearArgs a) {
+    constexpr int NT = 2;
+    __shared__ __align__(16) bf16 xs[16 * MT][tilemma::MMA_LDS];
+    __shared__ int row_s[16 * MT];
+    griddep_wait();
+    const int t0 = blockIdx.x * 16 * MT, h = blockIdx.y;
+    for (int i = threadIdx.x; i < 16 * MT; i += blockDim.x) row_s[i] = t0 + i < a.T ? t0 + i : -1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int c0 = (blockIdx.z * 8 + warp) * (8 * NT);
+    if (c0 >= a.n_out) {                                       // the warp has no columns; it still helps to stage the rows
+        const bf16* none[1][NT];
+#pragma unroll
+        for (int j = 0; j < NT; j++) none[0][j] = W + (size_t)h * a.n_out * a.n_in;
+        float acc[1][MT][NT][4];
+        tilemma::mma_tile<MT, NT, 1>(xs, row_s, in + (size_t)h * a.head_in + a.in_off, (size_t)a.ld_in, 1, none, a.n_in, acc);
+        return;
+    }
+    const bf16* wrow[1][NT];
+#pragma unroll
+    for (int j = 0; j < NT; j++) wrow[0][j] = W + ((size_t)h * a.n_out + min(c0 + j * 8 + g, a.n_out - 1)) * a.n_in;
+    float acc[1][MT][NT][4];
+    tilemma::mma_tile<MT, NT, 1>(xs, row_s, in + (size_t)h * a.head_in + a.in_off, (size_t)a.ld_in, 1, wrow, a.n_in, acc);
+#pragma unroll
+    for (int m = 0; m < MT; m++)
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int r = row_s[m * 16 + g + 8 * half];
+            if (r < 0) continue;
+            bf16* o = out + (size_t)r * a.ld_out + (size_t)h * a.head_out + a.out_off;
+#pragma unroll
+            for (int j = 0; j < NT; j++)
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    const int c = c0 + j * 8 + 2 * t + q;
+                    if (c < a.n_out) o[c] = from_f32<bf16>(acc[0][m][j][2 * half + q]);
+                }
+        }
+}
+
 }  // namespace
+
+// 1: bfloat16 per-head products run on the plain tiled kernel too (the tests compare the two).
+static int g_head_linear_plain = 0;
+MYNAH_API int mynah_head_linear_plain(int on) {
+    const int before = g_head_linear_plain;
+    g_head_linear_plain = on;
+    return before;
+}
 
 MYNAH_API int mynah_rope_table_freqs(float* cos_t, float* sin_t, int n_pos, int half, const double* freqs, double mult,
                                      cudaStream_t stream) {
@@ -199,6 +252,15 @@ MYNAH_API int mynah_head_linear(const void* in, const void* W, void* out, int dt
     MYNAH_REQUIRE(T > 0 && H > 0 && n_in > 0 && n_out > 0, "head_linear: bad sizes");
     MYNAH_REQUIRE(H <= 65535 && ceil_div(n_out, 64) <= 65535, "head_linear: too many heads or outputs for one launch");
     const HeadLinearArgs a{T, H, n_in, n_out, ld_in, head_in, in_off, ld_out, head_out, out_off};
+    const bool mma_ok = dtype == MYNAH_BF16 && !g_head_linear_plain && n_in % 8 == 0 && ld_in % 8 == 0 && head_in % 8 == 0 &&
+                        in_off % 8 == 0 && (((uintptr_t)in | (uintptr_t)W) & 15) == 0 && ceil_div(n_out, 128) <= 65535;
+    if (mma_ok) {
+        if (T <= 16)
+            mynah_launch(head_linear_mma_kernel<1>, dim3(1, H, ceil_div(n_out, 128)), dim3(256), 0, stream, (const bf16*)in, (const bf16*)W, (bf16*)out, a);
+        else
+            mynah_launch(head_linear_mma_kernel<4>, dim3(ceil_div(T, 64), H, ceil_div(n_out, 128)), dim3(256), 0, stream, (const bf16*)in, (const bf16*)W, (bf16*)out, a);
+        return mynah_check_launch("head_linear");
+    }
     const dim3 grid(ceil_div(T, 64), H, ceil_div(n_out, 64));
     if (dtype == MYNAH_F32)
         mynah_launch(head_linear_kernel<float>, grid, dim3(tilemm::THREADS), 0, stream, (const float*)in, (const float*)W, (float*)out, a);

@@ -14,6 +14,7 @@
 // beyond the step's tiles leave at once, so a captured step needs no count from the host.
 #include "layout.cuh"
 #include "tile_mm.cuh"
+#include "tile_mma.cuh"
 
 namespace {
 
@@ -158,81 +159,17 @@ __global__ void moe_combine_kernel(const float* __restrict__ o, const int* __res
     }
 }
 
-// ---- the bfloat16 products on tensor cores (mma.sync m16n8k16, fp32 accumulators) ----
-// A tile's rows (16 * MT of them, gathered through `perm`) pass through shared memory in blocks of MMA_KC values of k;
-// the expert's weights stream from global memory (or L2, for the tiles that share an expert) straight into the B
-// fragments, 16 bytes a lane: lane (g, t) of a warp takes values [t * 8, t * 8 + 8) of row g of a k-block of 32, which
-// feed two instructions. The instruction's k slots are thereby filled in another order than memory's; A is read from
-// shared memory in the same order (values [t * 8, t * 8 + 8) of rows g and g + 8), and a sum over k does not care.
-// Every output is one chain of instructions over ascending k-blocks whatever the tile, so a row's bits do not depend
-// on the other rows, nor on whether the step was a prompt (64-row tiles) or a decode step (16-row tiles).
-constexpr int MMA_KC = 256;
-constexpr int MMA_LDS = MMA_KC + 32;          // row stride in shared memory: 16 words off a multiple of 32 banks
-
-__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// acc[s][m][j]: stream s (one weight matrix each), m-th group of 16 rows, j-th group of 8 columns of this warp
-template <int MT, int NT, int NS>
-__device__ __forceinline__ void mma_tile(bf16 (*xs)[MMA_LDS], const int* pair_s, const bf16* __restrict__ src, size_t ld_src,
-                                         int src_div, const bf16* const (&wrow)[NS][NT], int K, float (&acc)[NS][MT][NT][4]) {
-    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-#pragma unroll
-    for (int s = 0; s < NS; s++)
-#pragma unroll
-        for (int m = 0; m < MT; m++)
-#pragma unroll
-            for (int j = 0; j < NT; j++)
-#pragma unroll
-                for (int e = 0; e < 4; e++) acc[s][m][j][e] = 0.f;
-    for (int k0 = 0; k0 < K; k0 += MMA_KC) {
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < 16 * MT * (MMA_KC / 8); idx += blockDim.x) {
-            const int r = idx / (MMA_KC / 8), kk = (idx % (MMA_KC / 8)) * 8;
-            const int p = pair_s[r];
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (p >= 0 && k0 + kk < K) v = *reinterpret_cast<const uint4*>(src + (size_t)(p / src_div) * ld_src + k0 + kk);
-            *reinterpret_cast<uint4*>(&xs[r][kk]) = v;
-        }
-        __syncthreads();
-        const int kend = min(MMA_KC, K - k0);
-#pragma unroll 2
-        for (int kb = 0; kb < kend; kb += 32) {
-            const bool in = kb + t * 8 < kend;                    // K is a multiple of 8: a lane's 8 values are all in or all out
-            uint4 b[NS][NT];
-#pragma unroll
-            for (int s = 0; s < NS; s++)
-#pragma unroll
-                for (int j = 0; j < NT; j++)
-                    b[s][j] = in ? __ldg(reinterpret_cast<const uint4*>(wrow[s][j] + k0 + kb + t * 8)) : make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-            for (int m = 0; m < MT; m++) {
-                const uint4 lo = *reinterpret_cast<const uint4*>(&xs[m * 16 + g][kb + t * 8]);
-                const uint4 hi = *reinterpret_cast<const uint4*>(&xs[m * 16 + g + 8][kb + t * 8]);
-#pragma unroll
-                for (int s = 0; s < NS; s++)
-#pragma unroll
-                    for (int j = 0; j < NT; j++) {
-                        mma_bf16(acc[s][m][j], lo.x, hi.x, lo.y, hi.y, b[s][j].x, b[s][j].y);
-                        mma_bf16(acc[s][m][j], lo.z, hi.z, lo.w, hi.w, b[s][j].z, b[s][j].w);
-                    }
-            }
-        }
-    }
-}
-
+// ---- the bfloat16 products on tensor cores (the core is in tile_mma.cuh) ----
+// A row's bits do not depend on whether the step was a prompt (64-row tiles) or a decode step (16-row tiles).
 constexpr int MMA_WARPS = 8;
 
-// grid (tiles, ceil(F / (8 warps * 16 columns))). A warp takes 16 columns of the gate and the same 16 of the up matrix.
-template <int MT>
+// grid (tiles, ceil(F / (8 warps * 8 NT columns))). A warp takes 8 NT columns of the gate and the same of the up matrix.
+// Decode steps (16-row tiles, mostly one row) take narrow warps, so that many CTAs stream the weights.
+template <int MT, int NT>
 __global__ void __launch_bounds__(MMA_WARPS * 32)
 moe_gate_up_mma_kernel(const bf16* __restrict__ h, const bf16* __restrict__ w_gu, bf16* __restrict__ y,
                        const int* __restrict__ perm, const int* __restrict__ tiles, MoeArgs a) {
-    constexpr int NT = 2;
-    __shared__ __align__(16) bf16 xs[16 * MT][MMA_LDS];
+    __shared__ __align__(16) bf16 xs[16 * MT][tilemma::MMA_LDS];
     __shared__ int pair_s[16 * MT];
     griddep_wait();
     if ((int)blockIdx.x >= tiles[0]) return;
@@ -248,7 +185,7 @@ moe_gate_up_mma_kernel(const bf16* __restrict__ h, const bf16* __restrict__ w_gu
         wrow[1][j] = wrow[0][j] + (size_t)a.F * a.D;
     }
     float acc[2][MT][NT][4];
-    mma_tile<MT, NT, 2>(xs, pair_s, h, (size_t)a.D, a.top, wrow, a.D, acc);
+    tilemma::mma_tile<MT, NT, 2>(xs, pair_s, h, (size_t)a.D, a.top, wrow, a.D, acc);
 #pragma unroll
     for (int m = 0; m < MT; m++)
 #pragma unroll
@@ -268,13 +205,12 @@ moe_gate_up_mma_kernel(const bf16* __restrict__ h, const bf16* __restrict__ w_gu
         }
 }
 
-// grid (tiles, ceil(D / (8 warps * 32 columns)))
-template <int MT>
+// grid (tiles, ceil(D / (8 warps * 8 NT columns)))
+template <int MT, int NT>
 __global__ void __launch_bounds__(MMA_WARPS * 32)
 moe_down_mma_kernel(const bf16* __restrict__ y, const bf16* __restrict__ w_down, float* __restrict__ o,
                     const int* __restrict__ perm, const int* __restrict__ tiles, MoeArgs a) {
-    constexpr int NT = 4;
-    __shared__ __align__(16) bf16 xs[16 * MT][MMA_LDS];
+    __shared__ __align__(16) bf16 xs[16 * MT][tilemma::MMA_LDS];
     __shared__ int pair_s[16 * MT];
     griddep_wait();
     if ((int)blockIdx.x >= tiles[0]) return;
@@ -286,7 +222,7 @@ moe_down_mma_kernel(const bf16* __restrict__ y, const bf16* __restrict__ w_down,
 #pragma unroll
     for (int j = 0; j < NT; j++) wrow[0][j] = w_down + ((size_t)e * a.D + min(c0 + j * 8 + g, a.D - 1)) * a.F;
     float acc[1][MT][NT][4];
-    mma_tile<MT, NT, 1>(xs, pair_s, y, (size_t)a.F, 1, wrow, a.F, acc);
+    tilemma::mma_tile<MT, NT, 1>(xs, pair_s, y, (size_t)a.F, 1, wrow, a.F, acc);
 #pragma unroll
     for (int m = 0; m < MT; m++)
 #pragma unroll
@@ -306,10 +242,11 @@ moe_down_mma_kernel(const bf16* __restrict__ y, const bf16* __restrict__ w_down,
 template <int MT>
 int launch_products_mma(const void* h, const void* w_gu, const void* w_down, void* y, float* o, const int* perm,
                         const int* tiles, int max_tiles, const MoeArgs& a, cudaStream_t stream) {
-    mynah_launch(moe_gate_up_mma_kernel<MT>, dim3(max_tiles, ceil_div(a.F, MMA_WARPS * 16)), dim3(MMA_WARPS * 32), 0, stream,
+    constexpr int NT_GU = MT == 1 ? 1 : 2, NT_DOWN = MT == 1 ? 1 : 4;
+    mynah_launch(moe_gate_up_mma_kernel<MT, NT_GU>, dim3(max_tiles, ceil_div(a.F, MMA_WARPS * 8 * NT_GU)), dim3(MMA_WARPS * 32), 0, stream,
                  (const bf16*)h, (const bf16*)w_gu, (bf16*)y, perm, tiles, a);
     if (mynah_check_launch("moe_gate_up") != 0) return -1;
-    mynah_launch(moe_down_mma_kernel<MT>, dim3(max_tiles, ceil_div(a.D, MMA_WARPS * 32)), dim3(MMA_WARPS * 32), 0, stream,
+    mynah_launch(moe_down_mma_kernel<MT, NT_DOWN>, dim3(max_tiles, ceil_div(a.D, MMA_WARPS * 8 * NT_DOWN)), dim3(MMA_WARPS * 32), 0, stream,
                  (const bf16*)y, (const bf16*)w_down, o, perm, tiles, a);
     return mynah_check_launch("moe_down");
 }

@@ -185,8 +185,9 @@ retention_chunk_kernel(const float* __restrict__ qn, const float* __restrict__ k
     float* qs = sm;                        // [C][ldr]
     float* ks = qs + C * ldr;              // [C][ldr]
     float* Ss = ks + C * ldr;              // [d][32]
-    float* Ws = Ss + d * RC_JW;            // [C][C + 1]
-    float* vs = Ws + C * (C + 1);          // [C][32]
+    constexpr int LDW = C + 4;             // row stride of the decayed scores (rows stay 16-byte aligned)
+    float* Ws = Ss + d * RC_JW;            // [C][LDW]
+    float* vs = Ws + C * LDW;              // [C][32]
     float* gp = vs + C * RC_JW;            // [C + 1]: powers of the decay
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int j = blockIdx.x * RC_JW + lane;
@@ -252,7 +253,7 @@ retention_chunk_kernel(const float* __restrict__ qn, const float* __restrict__ k
 #pragma unroll
                 for (int w = 0; w < TT; w++) {
                     const int t = ta + 16 * u, s = sb + 16 * w;
-                    Ws[t * (C + 1) + s] = s <= t ? gp[t - s] * acc[u][w] : 0.f;
+                    Ws[t * LDW + s] = s <= t ? gp[t - s] * acc[u][w] : 0.f;
                 }
         }
         __syncthreads();
@@ -261,11 +262,18 @@ retention_chunk_kernel(const float* __restrict__ qn, const float* __restrict__ k
 #pragma unroll
             for (int u = 0; u < TPW; u++) intra[u] = inter[u] = 0.f;
             const int tb = warp * TPW;
-            const int s_end = min(tb + TPW, nt);                 // keys beyond the warp's last token weigh nothing
-            for (int s = 0; s < s_end; s++) {
-                const float vv = vs[s * RC_JW + lane];
+            const int s_end = min(tb + TPW, C);                  // keys beyond the warp's last token weigh nothing
+            for (int s = 0; s < s_end; s += 4) {                 // (TPW is a multiple of 4; rows beyond nt hold zeros)
+                const float v0 = vs[s * RC_JW + lane], v1 = vs[(s + 1) * RC_JW + lane];
+                const float v2 = vs[(s + 2) * RC_JW + lane], v3 = vs[(s + 3) * RC_JW + lane];
 #pragma unroll
-                for (int u = 0; u < TPW; u++) intra[u] = fmaf(Ws[(tb + u) * (C + 1) + s], vv, intra[u]);
+                for (int u = 0; u < TPW; u++) {
+                    const float4 w4 = *reinterpret_cast<const float4*>(Ws + (tb + u) * LDW + s);
+                    intra[u] = fmaf(w4.x, v0, intra[u]);
+                    intra[u] = fmaf(w4.y, v1, intra[u]);
+                    intra[u] = fmaf(w4.z, v2, intra[u]);
+                    intra[u] = fmaf(w4.w, v3, intra[u]);
+                }
             }
             for (int i = 0; i < d; i += 4) {
                 const float s0 = Ss[i * RC_JW + lane], s1 = Ss[(i + 1) * RC_JW + lane];
@@ -290,22 +298,29 @@ retention_chunk_kernel(const float* __restrict__ qn, const float* __restrict__ k
         __syncthreads();                                         // every warp has read the old state
         {   // the state's rows warp * rpw + r, column `lane`
             const float gn = gp[nt];
-            for (int r0 = 0; r0 < rpw; r0 += 4) {
-                const int i = warp * rpw + r0;
-                float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-                for (int s = 0; s < nt; s++) {
-                    const float vw = gp[nt - 1 - s] * vs[s * RC_JW + lane];
-                    const float4 kv = *reinterpret_cast<const float4*>(ks + s * ldr + i);
-                    l0 = fmaf(kv.x, vw, l0);
-                    l1 = fmaf(kv.y, vw, l1);
-                    l2 = fmaf(kv.z, vw, l2);
-                    l3 = fmaf(kv.w, vw, l3);
+            float loc[32];                                       // rpw <= 32 rows (d <= 256)
+#pragma unroll
+            for (int r = 0; r < 32; r++) loc[r] = 0.f;
+            const float* kw = ks + warp * rpw;
+            for (int s = 0; s < nt; s++) {
+                const float vw = gp[nt - 1 - s] * vs[s * RC_JW + lane];
+#pragma unroll
+                for (int r4 = 0; r4 < 8; r4++) {
+                    if (r4 * 4 < rpw) {
+                        const float4 kv = *reinterpret_cast<const float4*>(kw + s * ldr + r4 * 4);
+                        loc[r4 * 4] = fmaf(kv.x, vw, loc[r4 * 4]);
+                        loc[r4 * 4 + 1] = fmaf(kv.y, vw, loc[r4 * 4 + 1]);
+                        loc[r4 * 4 + 2] = fmaf(kv.z, vw, loc[r4 * 4 + 2]);
+                        loc[r4 * 4 + 3] = fmaf(kv.w, vw, loc[r4 * 4 + 3]);
+                    }
                 }
-                Ss[i * RC_JW + lane] = fmaf(gn, Ss[i * RC_JW + lane], l0);
-                Ss[(i + 1) * RC_JW + lane] = fmaf(gn, Ss[(i + 1) * RC_JW + lane], l1);
-                Ss[(i + 2) * RC_JW + lane] = fmaf(gn, Ss[(i + 2) * RC_JW + lane], l2);
-                Ss[(i + 3) * RC_JW + lane] = fmaf(gn, Ss[(i + 3) * RC_JW + lane], l3);
             }
+#pragma unroll
+            for (int r = 0; r < 32; r++)
+                if (r < rpw) {
+                    float* sl = Ss + (warp * rpw + r) * RC_JW + lane;
+                    *sl = fmaf(gn, *sl, loc[r]);
+                }
         }
     }
     __syncthreads();
@@ -319,7 +334,7 @@ template <typename T, int C>
 int launch_chunked(const float* qn, const float* kn, const void* v, const float* decay, float* state, float* o,
                    const int* cu_q, const int* slots, int B, const RetChunkArgs& a, cudaStream_t stream) {
     const int d = a.dim;
-    const size_t smem = ((size_t)2 * C * (d + 4) + (size_t)d * RC_JW + (size_t)C * (C + 1) + (size_t)C * RC_JW + C + 1 + 3) * sizeof(float);
+    const size_t smem = ((size_t)2 * C * (d + 4) + (size_t)d * RC_JW + (size_t)C * (C + 4) + (size_t)C * RC_JW + C + 1 + 3) * sizeof(float);
     if (cudaFuncSetAttribute(retention_chunk_kernel<T, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return mynah_fail("retention_scan: %zu bytes of shared memory are not to be had", smem);
     mynah_launch(retention_chunk_kernel<T, C>, dim3(ceil_div(a.vd, RC_JW), a.H, B), dim3(RC_THREADS), smem, stream,

@@ -905,6 +905,12 @@ def retention_chunk_min(n: int) -> int:
     return int(lib.load().mynah_retention_chunk_min(int(n)))
 
 
+def head_linear_plain(on: bool) -> bool:
+    """Run the bfloat16 per-head products on the plain tiled kernel instead of the tensor-core one (the tests compare the
+    two). Returns the setting before."""
+    return bool(lib.load().mynah_head_linear_plain(1 if on else 0))
+
+
 def moe_plain(on: bool) -> bool:
     """Run the experts' bfloat16 products on the plain tiled kernels instead of the tensor-core ones (the tests compare
     the two). Returns the setting before."""

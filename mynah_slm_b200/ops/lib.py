@@ -159,7 +159,7 @@ def load() -> ctypes.CDLL:
     lib.mynah_gemm_tcgen05_splits_k.argtypes = [c_int, c_int, c_int, c_int]
     lib.mynah_gemv_decode_supported.restype = c_int
     lib.mynah_gemv_decode_supported.argtypes = [c_int, c_int, c_int]
-    for name in ("mynah_moe_plain", "mynah_retention_chunk_min"):
+    for name in ("mynah_moe_plain", "mynah_retention_chunk_min", "mynah_head_linear_plain"):
         getattr(lib, name).restype = c_int
         getattr(lib, name).argtypes = [c_int]
     lib.mynah_moe_max_tiles.restype = c_int

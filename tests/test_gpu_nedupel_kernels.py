@@ -94,11 +94,13 @@ def test_latent_prep_and_cache_rows(H, dim, rd, r, interleaved):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,H,n_in,n_out", [(70, 3, 16, 40), (1, 1, 6, 13), (130, 5, 100, 70)])
-def test_head_linear(dtype, T, H, n_in, n_out):
+@pytest.mark.parametrize("T,H,n_in,n_out,aligned", [(70, 3, 16, 40, True), (1, 1, 6, 13, False), (130, 5, 100, 70, False),
+                                                    (9, 2, 64, 150, True), (200, 3, 96, 96, True)])
+def test_head_linear(dtype, T, H, n_in, n_out, aligned):
     from mynah_slm_b200.ops import kernels
     rng = np.random.default_rng(T + n_in)
-    head_in, in_off, head_out, out_off = n_in + 5, 3, n_out + 9, 2
+    # aligned: heads start at multiples of 8 values (what the tensor-core form needs in bfloat16); else anywhere
+    head_in, in_off, head_out, out_off = (n_in + 8, 8, n_out + 9, 2) if aligned else (n_in + 5, 3, n_out + 9, 2)
     x = torch.tensor(rng.normal(size=(T, H * head_in)), dtype=dtype, device=DEV)
     W = torch.tensor(rng.normal(size=(H, n_out, n_in)), dtype=dtype, device=DEV)
     out = torch.full((T, H * head_out), 7.0, dtype=dtype, device=DEV)
@@ -108,6 +110,18 @@ def test_head_linear(dtype, T, H, n_in, n_out):
     got = out.double().cpu().numpy().reshape(T, H, head_out)
     assert rel(ref, got[..., out_off:out_off + n_out]) < (1e-5 if dtype == torch.float32 else 1e-2)
     assert np.all(got[..., :out_off] == 7.0) and np.all(got[..., out_off + n_out:] == 7.0)
+    if dtype == torch.bfloat16 and aligned:
+        before = kernels.head_linear_plain(True)
+        try:
+            out2 = torch.full((T, H * head_out), 7.0, dtype=dtype, device=DEV)
+            kernels.head_linear(x, head_in, in_off, W, out2, head_out, out_off)
+        finally:
+            kernels.head_linear_plain(before)
+        assert rel(out2.double().cpu().numpy(), out.double().cpu().numpy()) < 1e-2
+        # a row's bits in a small step (16-row tiles) and in a large one (64-row tiles)
+        few = torch.full((3, H * head_out), 7.0, dtype=dtype, device=DEV)
+        kernels.head_linear(x[:3].contiguous(), head_in, in_off, W, few, head_out, out_off)
+        assert torch.equal(few, out[:3])
 
 
 def plain_retention_core(q, k, v, decay, S0=None):
