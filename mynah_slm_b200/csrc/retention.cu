@@ -232,6 +232,7 @@ retention_chunk_kernel(const float* __restrict__ qn, const float* __restrict__ k
             for (int u = 0; u < TT; u++)
 #pragma unroll
                 for (int w = 0; w < TT; w++) acc[u][w] = 0.f;
+#pragma unroll 2
             for (int i = 0; i < d; i += 4) {
                 float4 qv[TT], kv[TT];
 #pragma unroll
@@ -275,6 +276,7 @@ retention_chunk_kernel(const float* __restrict__ qn, const float* __restrict__ k
                     intra[u] = fmaf(w4.w, v3, intra[u]);
                 }
             }
+#pragma unroll 2
             for (int i = 0; i < d; i += 4) {
                 const float s0 = Ss[i * RC_JW + lane], s1 = Ss[(i + 1) * RC_JW + lane];
                 const float s2 = Ss[(i + 2) * RC_JW + lane], s3 = Ss[(i + 3) * RC_JW + lane];
@@ -302,6 +304,7 @@ retention_chunk_kernel(const float* __restrict__ qn, const float* __restrict__ k
 #pragma unroll
             for (int r = 0; r < 32; r++) loc[r] = 0.f;
             const float* kw = ks + warp * rpw;
+#pragma unroll 2
             for (int s = 0; s < nt; s++) {
                 const float vw = gp[nt - 1 - s] * vs[s * RC_JW + lane];
 #pragma unroll
