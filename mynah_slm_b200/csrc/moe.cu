@@ -166,7 +166,7 @@ constexpr int MMA_WARPS = 8;
 // grid (tiles, ceil(F / (8 warps * 8 NT columns))). A warp takes 8 NT columns of the gate and the same of the up matrix.
 // Decode steps (16-row tiles, mostly one row) take narrow warps, so that many CTAs stream the weights.
 template <int MT, int NT>
-__global__ void __launch_bounds__(MMA_WARPS * 32)
+__global__ void __launch_bounds__(MMA_WARPS * 32, 2)
 moe_gate_up_mma_kernel(const bf16* __restrict__ h, const bf16* __restrict__ w_gu, bf16* __restrict__ y,
                        const int* __restrict__ perm, const int* __restrict__ tiles, MoeArgs a) {
     __shared__ __align__(16) bf16 xs[16 * MT][tilemma::MMA_LDS];
@@ -207,7 +207,7 @@ moe_gate_up_mma_kernel(const bf16* __restrict__ h, const bf16* __restrict__ w_gu
 
 // grid (tiles, ceil(D / (8 warps * 8 NT columns)))
 template <int MT, int NT>
-__global__ void __launch_bounds__(MMA_WARPS * 32)
+__global__ void __launch_bounds__(MMA_WARPS * 32, 2)
 moe_down_mma_kernel(const bf16* __restrict__ y, const bf16* __restrict__ w_down, float* __restrict__ o,
                     const int* __restrict__ perm, const int* __restrict__ tiles, MoeArgs a) {
     __shared__ __align__(16) bf16 xs[16 * MT][tilemma::MMA_LDS];

@@ -17,7 +17,7 @@ constexpr int MMA_KC = 256;
 constexpr int MMA_LDS = MMA_KC + 32;          // row stride in shared memory: 16 words off a multiple of 32 banks
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -46,28 +46,46 @@ __device__ __forceinline__ void mma_tile(bf16 (*xs)[MMA_LDS], const int* row_s, 
         }
         __syncthreads();
         const int kend = min(MMA_KC, K - k0);
-        constexpr int UNROLL = MT == 1 ? 4 : 2;                   // a small tile has registers for more loads in flight
-#pragma unroll UNROLL
-        for (int kb = 0; kb < kend; kb += 32) {
-            const bool in = kb + t * 8 < kend;                    // K is a multiple of 8: a lane's 8 values are all in or all out
-            uint4 b[NS][NT];
+        // the weights of the k-blocks after the ones being multiplied are already on their way: one block ahead under
+        // a tall tile (registers are the accumulators'), four under a 16-row tile (a decode step lives on loads in flight)
+        constexpr int DEPTH = MT == 1 ? 4 : 1;
+        auto fetch = [&](int kb, uint4 (&b)[DEPTH][NS][NT]) {
 #pragma unroll
-            for (int s = 0; s < NS; s++)
-#pragma unroll
-                for (int j = 0; j < NT; j++)
-                    b[s][j] = in ? __ldg(reinterpret_cast<const uint4*>(wrow[s][j] + k0 + kb + t * 8)) : make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-            for (int m = 0; m < MT; m++) {
-                const uint4 lo = *reinterpret_cast<const uint4*>(&xs[m * 16 + g][kb + t * 8]);
-                const uint4 hi = *reinterpret_cast<const uint4*>(&xs[m * 16 + g + 8][kb + t * 8]);
+            for (int dd = 0; dd < DEPTH; dd++) {
+                const bool in = kb + 32 * dd + t * 8 < kend;      // K is a multiple of 8: a lane's 8 values are all in or all out
 #pragma unroll
                 for (int s = 0; s < NS; s++)
 #pragma unroll
-                    for (int j = 0; j < NT; j++) {
-                        mma_bf16(acc[s][m][j], lo.x, hi.x, lo.y, hi.y, b[s][j].x, b[s][j].y);
-                        mma_bf16(acc[s][m][j], lo.z, hi.z, lo.w, hi.w, b[s][j].z, b[s][j].w);
-                    }
+                    for (int j = 0; j < NT; j++)
+                        b[dd][s][j] = in ? __ldg(reinterpret_cast<const uint4*>(wrow[s][j] + k0 + kb + 32 * dd + t * 8))
+                                         : make_uint4(0u, 0u, 0u, 0u);
             }
+        };
+        uint4 b[DEPTH][NS][NT], bn[DEPTH][NS][NT];
+        fetch(0, b);
+        for (int kb = 0; kb < kend; kb += 32 * DEPTH) {
+            fetch(kb + 32 * DEPTH, bn);                           // beyond the block: zeros, not used
+#pragma unroll
+            for (int dd = 0; dd < DEPTH; dd++) {                  // (blocks beyond kend multiply zeros; they stay inside xs)
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    const uint4 lo = *reinterpret_cast<const uint4*>(&xs[m * 16 + g][kb + 32 * dd + t * 8]);
+                    const uint4 hi = *reinterpret_cast<const uint4*>(&xs[m * 16 + g + 8][kb + 32 * dd + t * 8]);
+#pragma unroll
+                    for (int s = 0; s < NS; s++)
+#pragma unroll
+                        for (int j = 0; j < NT; j++) {
+                            mma_bf16(acc[s][m][j], lo.x, hi.x, lo.y, hi.y, b[dd][s][j].x, b[dd][s][j].y);
+                            mma_bf16(acc[s][m][j], lo.z, hi.z, lo.w, hi.w, b[dd][s][j].z, b[dd][s][j].w);
+                        }
+                }
+            }
+#pragma unroll
+            for (int dd = 0; dd < DEPTH; dd++)
+#pragma unroll
+                for (int s = 0; s < NS; s++)
+#pragma unroll
+                    for (int j = 0; j < NT; j++) b[dd][s][j] = bn[dd][s][j];
         }
     }
 }

@@ -893,8 +893,13 @@ def retention_scan(qn: torch.Tensor, kn: torch.Tensor, v: torch.Tensor, v_off: i
         raise KernelError("retention_scan: the value rows are too short")
     T = v.shape[0]
     o = torch.empty((T, H * vd), dtype=torch.float32, device=v.device)
+    need = int(lib.load().mynah_retention_scratch_floats(T, H, dim, int(ctx.max_q_len)))      # the chunked form's scores
+    scratch = torch.empty((need,), dtype=torch.float32, device=v.device) if need else None
     call("mynah_retention_scan", ptr(qn), ptr(kn), ptr(v), v.stride(0), v_off, code(v.dtype), ptr(decay), ptr(state),
-         state.shape[0] - 1, ptr(o), ptr(ctx.cu_q), ptr(ctx.slots), ctx.B, H, dim, vd, int(ctx.max_q_len), stream_ptr())
+         state.shape[0] - 1, ptr(o), ptr(ctx.cu_q), ptr(ctx.slots), ctx.B, H, dim, vd, int(ctx.max_q_len), T, ptr(scratch),
+         stream_ptr())
+    if need:
+        lib.add_launches(1)
     return o
 
 

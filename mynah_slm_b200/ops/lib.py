@@ -115,7 +115,7 @@ _SIGNATURES: dict[str, list] = {
     "mynah_head_linear": [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P],
     "mynah_retention_prep": [P, c_int, c_int, c_int, c_int, P, P, c_int, c_int, c_int, P, P, c_int, c_int, c_int,
                              c_float, P, P, P, P],
-    "mynah_retention_scan": [P, P, P, c_int, c_int, c_int, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
+    "mynah_retention_scan": [P, P, P, c_int, c_int, c_int, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
     "mynah_moe_table_ffn": [P, c_int, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_float, c_float, c_float, P, P],
 }
@@ -162,6 +162,8 @@ def load() -> ctypes.CDLL:
     for name in ("mynah_moe_plain", "mynah_retention_chunk_min", "mynah_head_linear_plain"):
         getattr(lib, name).restype = c_int
         getattr(lib, name).argtypes = [c_int]
+    lib.mynah_retention_scratch_floats.restype = c_longlong
+    lib.mynah_retention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mynah_moe_max_tiles.restype = c_int
     lib.mynah_moe_max_tiles.argtypes = [c_int, c_int, c_int]
     for name, args in _SIGNATURES.items():
