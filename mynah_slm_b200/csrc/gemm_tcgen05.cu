@@ -39,7 +39,11 @@ constexpr int A_BYTES = BM * BK * 2;                 // 16 KB
 constexpr int THREADS = 192;
 constexpr int STAGING_BYTES = 32 * 128;              // 32 rows x 128 bytes per epilogue warp and buffer
 
-enum Epi : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV = 3 };
+enum Epi : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV = 3, EPI_GATED = 4 };
+
+// The two epilogues that read a gate tile and its up tile side by side: SwiGLU, and the clamped gate
+// g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha g) * (u + 1).
+__host__ __device__ constexpr bool epi_glu(int epi) { return epi == EPI_SWIGLU || epi == EPI_GATED; }
 
 // Shared-memory operand descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
@@ -106,6 +110,11 @@ struct GemmShape {
     int m_tiles, n_tiles; // m_tiles: tiles of 128 rows (one CTA) or 256 rows (a pair of CTAs)
     float* sk_part;       // with SK: a CTA's partial accumulator, [CTAs][128][BN] fp32
     int* sk_flag;         // with SK: [CTAs][4], set by the warp that wrote its 32 rows, cleared by the warp that read them
+    // Grouped products (single CTAs only): W stacks several matrices of group_rows rows each, and row tile m of A
+    // multiplies matrix tile_group[m] (rows of A sorted by matrix, every matrix's rows padded to whole tiles). null: one W.
+    const int* tile_group;
+    int group_rows;
+    float gate_limit, gate_alpha;   // of the clamped gate epilogue
 };
 
 // What a unit works on next: a tile of C and a range of its k-blocks. Without SK that is a whole tile (or, with
@@ -223,7 +232,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     constexpr int B_BYTES = BN * BK * 2 / CTAS;                      // this CTA's rows of W
     constexpr int STAGE = A_BYTES + B_BYTES;
     constexpr int STAGES = ring_stages(BN, CTAS);
-    constexpr int OUT_COLS = EPI == EPI_SWIGLU ? 128 : BN;           // output columns of a tile
+    constexpr int OUT_COLS = epi_glu(EPI) ? 128 : BN;                // output columns of a tile
     constexpr int CHUNK = EPI == EPI_F32 ? 32 : 64;                  // output columns per staged store (128 bytes per row)
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -316,7 +325,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         // both CTAs' copies complete on the leader's barrier, which expects the bytes of both
                         if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE);
                         tma_load_2d_pair(a_dst, &map_a, kb * BK, (m_tile * 2 + rank) * BM, full0 + 8 * s);
-                        const int w_row = EPI == EPI_SWIGLU ? (rank == 0 ? n_tile * 128 : g.up_offset + n_tile * 128)
+                        const int w_row = epi_glu(EPI) ? (rank == 0 ? n_tile * 128 : g.up_offset + n_tile * 128)
                                                             : n_tile * BN + rank * (BN / 2);
                         tma_load_2d_pair(b_dst, &map_b, kb * BK, w_row, full0 + 8 * s);
                         continue;
@@ -326,13 +335,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (it == 1) GSTAMP(3, 0, 1);
                     tma_load_2d(a_dst, &map_a, kb * BK, m_tile * BM, full0 + 8 * s);
                     if (it == 1) GSTAMP(3, 0, 2);
-                    if (EPI == EPI_SWIGLU) {                         // 128 gate rows, then their 128 up rows
-                        tma_load_2d(b_dst, &map_b, kb * BK, n_tile * 128, full0 + 8 * s);
-                        tma_load_2d(b_dst + 128 * BK * 2, &map_b, kb * BK, g.up_offset + n_tile * 128, full0 + 8 * s);
+                    // (a grouped product: the rows of this row tile's own matrix inside the stacked W)
+                    const int wb = g.tile_group != nullptr ? g.tile_group[m_tile] * g.group_rows : 0;
+                    if (epi_glu(EPI)) {                              // 128 gate rows, then their 128 up rows
+                        tma_load_2d(b_dst, &map_b, kb * BK, wb + n_tile * 128, full0 + 8 * s);
+                        tma_load_2d(b_dst + 128 * BK * 2, &map_b, kb * BK, wb + g.up_offset + n_tile * 128, full0 + 8 * s);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BN / 128; j++)
-                            tma_load_2d(b_dst + j * 128 * BK * 2, &map_b, kb * BK, n_tile * BN + j * 128, full0 + 8 * s);
+                            tma_load_2d(b_dst + j * 128 * BK * 2, &map_b, kb * BK, wb + n_tile * BN + j * 128, full0 + 8 * s);
                     }
                     if (it == 1) GSTAMP(3, 0, 3);
                 }
@@ -600,7 +611,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         for (int e = 0; e < 32; e++) {
                             // gate and up rounded to bf16 first, as when they are stored before the activation
                             const float gv = round_to<bf16>(__uint_as_float(gt[e])), uv = round_to<bf16>(__uint_as_float(up[e]));
-                            o[e] = (gv * sigmoid_stable(gv)) * uv;
+                            if (EPI == EPI_GATED) {
+                                const float gc = fminf(gv, g.gate_limit), uc = fminf(fmaxf(uv, -g.gate_limit), g.gate_limit);
+                                o[e] = gc * (1.0f / (1.0f + expf(-g.gate_alpha * gc))) * (uc + 1.0f);
+                            } else
+                                o[e] = (gv * sigmoid_stable(gv)) * uv;
                         }
 #pragma unroll
                         for (int j = 0; j < 4; j++) {
@@ -746,7 +761,8 @@ int sk_workspace(int n_ctas, float** part, int** flag) {
 
 template <int BN, int EPI, int CTAS, int KS = 1, bool SK = false>
 int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, int M, int N, int K, int up_offset,
-                int sm_count, int* status, cudaStream_t stream, const QkvEpilogue& qe = QkvEpilogue{}) {
+                int sm_count, int* status, cudaStream_t stream, const QkvEpilogue& qe = QkvEpilogue{},
+                const int* tile_group = nullptr, int group_rows = 0, float gate_limit = 0.f, float gate_alpha = 0.f) {
     constexpr int STAGES = ring_stages(BN, CTAS);
     constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2 / CTAS) + 4 * 2 * STAGING_BYTES + 256 + 1024;
     auto kern = gemm_tcgen05_kernel<BN, EPI, CTAS, KS, SK>;
@@ -759,7 +775,9 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap&
     GemmShape g;
     g.M = M; g.N = N; g.K = K; g.up_offset = up_offset;
     g.m_tiles = ceil_div(M, BM * CTAS);
-    g.n_tiles = EPI == EPI_SWIGLU ? ceil_div(N, 128) : ceil_div(N, BN);
+    g.n_tiles = epi_glu(EPI) ? ceil_div(N, 128) : ceil_div(N, BN);
+    g.tile_group = tile_group; g.group_rows = group_rows; g.gate_limit = gate_limit; g.gate_alpha = gate_alpha;
+    static_assert(CTAS == 1 || EPI != EPI_GATED, "the grouped products run on single CTAs");
     const long long tiles = (long long)g.m_tiles * g.n_tiles;
     MYNAH_REQUIRE(tiles < (1ll << 30), "gemm_tcgen05: too many tiles");
     const int max_units = sm_count / (CTAS * KS);
@@ -899,6 +917,35 @@ MYNAH_API int mynah_gemm_tcgen05(const void* A, const void* W, void* C, int M, i
     if (epilogue == EPI_F32) return wide ? MYNAH_GEMM_GO(256, EPI_F32) : MYNAH_GEMM_GO(128, EPI_F32);
     return wide ? MYNAH_GEMM_GO(256, EPI_BF16) : MYNAH_GEMM_GO(128, EPI_BF16);
 #undef MYNAH_GEMM_GO
+}
+
+// Grouped product: W stacks `groups` matrices of group_rows rows each ([groups * group_rows, K]); the rows of A are sorted
+// by matrix and every matrix's rows padded to whole tiles of 128, and tile_group[m] (device, M / 128 entries) names the
+// matrix of row tile m. epilogue 1: C fp32 [M, N], N <= group_rows output columns of the tile's matrix; 4: the clamped
+// gate, a matrix being N gate rows then N up rows (group_rows = 2 N), C bf16 [M, N]. M must be a multiple of 128.
+MYNAH_API int mynah_gemm_tcgen05_grouped(const void* A, const void* W, void* C, int M, int N, int K, int ldc, int epilogue,
+                                         int groups, int group_rows, const int* tile_group, float gate_limit,
+                                         float gate_alpha, int sm_count, int* status, cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    MYNAH_REQUIRE(mynah_gemm_tcgen05_supported(M, N, K) && M % BM == 0, "gemm_tcgen05_grouped: M=%d N=%d K=%d is not taken", M, N, K);
+    MYNAH_REQUIRE((epilogue == EPI_F32 || epilogue == EPI_GATED) && ldc >= N, "gemm_tcgen05_grouped: bad epilogue or output stride");
+    MYNAH_REQUIRE(groups > 0 && tile_group != nullptr && group_rows >= (epilogue == EPI_GATED ? 2 * N : N),
+                  "gemm_tcgen05_grouped: the matrices do not hold the product's rows");
+    const int csize = epilogue == EPI_F32 ? 4 : 2;
+    MYNAH_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && ((uintptr_t)C & 15) == 0 && (ldc * csize) % 16 == 0,
+                  "gemm_tcgen05_grouped: operands must be 16-byte aligned and the output pitch a multiple of 16 bytes");
+    MYNAH_REQUIRE(status != nullptr, "gemm_tcgen05_grouped: a status word is required");
+    if (sm_count <= 0) sm_count = mynah_sm_count();
+    CUtensorMap ma, mb, mc;
+    if (make_map(&ma, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, K, 128, BK)) return -1;
+    if (make_map(&mb, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)groups * group_rows, K, K, 128, BK)) return -1;
+    if (epilogue == EPI_F32) {
+        if (make_map(&mc, C, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, ldc, 32, 32)) return -1;
+        return launch_gemm<256, EPI_F32, 1>(ma, mb, mc, M, N, K, 0, sm_count, status, stream, QkvEpilogue{}, tile_group, group_rows);
+    }
+    if (make_map(&mc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldc, 32, 64)) return -1;
+    return launch_gemm<256, EPI_GATED, 1>(ma, mb, mc, M, N, K, N, sm_count, status, stream, QkvEpilogue{}, tile_group, group_rows,
+                                          gate_limit, gate_alpha);
 }
 
 // The q/k/v projection of a prompt step with its epilogue: C = A . W^T as above (W rows: H heads of q, KV of k,

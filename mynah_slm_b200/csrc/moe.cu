@@ -10,6 +10,8 @@
 //   moe_down      for every tile: W_down,e y, written per pair in fp32
 //   moe_combine   out[t] = weight * sum over the token's pairs, in the order of its choices
 //
+// Prompt steps in bfloat16 take another route to the same result: see "prompts in bfloat16" below.
+//
 // The grid of the two products covers the most tiles a step can have (pairs / rows-per-tile + experts); CTAs
 // beyond the step's tiles leave at once, so a captured step needs no count from the host.
 #include "layout.cuh"
@@ -251,6 +253,85 @@ int launch_products_mma(const void* h, const void* w_gu, const void* w_down, voi
     return mynah_check_launch("moe_down");
 }
 
+// ---- prompts in bfloat16: the products as ONE grouped tcgen05 product each (gemm_tcgen05.cu) ----
+// The pairs are sorted by expert with every expert's rows padded to whole tiles of 128 (rows that hold no pair are
+// zeros), the token rows are gathered into that order, and the library's tensor-core kernel multiplies row tile m by the
+// matrix of tile_group[m]: the gate/up product with the clamped gate in its epilogue, then the down product.
+constexpr int GROUP_TILE = 128;
+
+__global__ void __launch_bounds__(MOE_ROUTE_THREADS)
+moe_route_padded_kernel(const int* __restrict__ tokens, const int* __restrict__ tok_seq, const int* __restrict__ table,
+                        int T, int V, int top, int E, int m_pad, int* __restrict__ pair_expert, int* __restrict__ row_of_pair,
+                        int* __restrict__ perm_pad, int* __restrict__ tile_group, int* __restrict__ status) {
+    __shared__ int count[MOE_MAX_EXPERTS], start[MOE_MAX_EXPERTS];
+    griddep_wait();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    for (int r = threadIdx.x; r < m_pad; r += blockDim.x) perm_pad[r] = -1;
+    __syncthreads();
+    const int P = T * top;
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int t = p / top;
+        int e = -1;
+        if (tok_seq[t] >= 0) {
+            const int tok = tokens[t];
+            if (tok >= 0 && tok < V) e = table[(size_t)tok * top + p % top];
+            if (e < 0 || e >= E) {
+                atomicOr(status, MYNAH_ST_TOKEN_RANGE);
+                e = -1;
+            }
+        }
+        pair_expert[p] = e;
+        if (e >= 0) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        const int n_tiles = m_pad / GROUP_TILE;
+        for (int e = 0; e < E; e++) {
+            start[e] = at;
+            for (int r = 0; r < count[e]; r += GROUP_TILE, at += GROUP_TILE)
+                if (at / GROUP_TILE < n_tiles) tile_group[at / GROUP_TILE] = e;
+        }
+        for (int tile = at / GROUP_TILE; tile < n_tiles; tile++) tile_group[tile] = 0;      // tiles of zeros: any matrix
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int e = pair_expert[p];
+        if (e < 0) continue;
+        const int row = start[e] + atomicAdd(&count[e], 1);
+        if (row < m_pad) {
+            perm_pad[row] = p;
+            row_of_pair[p] = row;
+        }
+    }
+}
+
+// a[r, :] = h[perm_pad[r] / top, :], zeros for the rows that hold no pair; 16 bytes a thread
+__global__ void moe_gather_kernel(const bf16* __restrict__ h, const int* __restrict__ perm_pad, bf16* __restrict__ a, int top, int D) {
+    griddep_wait();
+    const int r = blockIdx.x, p = perm_pad[r];
+    const uint4* src = p >= 0 ? reinterpret_cast<const uint4*>(h + (size_t)(p / top) * D) : nullptr;
+    uint4* dst = reinterpret_cast<uint4*>(a + (size_t)r * D);
+    for (int i = threadIdx.x; i < D / 8; i += blockDim.x) dst[i] = src != nullptr ? src[i] : make_uint4(0u, 0u, 0u, 0u);
+}
+
+__global__ void moe_combine_rows_kernel(const float* __restrict__ o, const int* __restrict__ pair_expert,
+                                        const int* __restrict__ row_of_pair, bf16* __restrict__ out, int top, int D, float weight) {
+    griddep_launch_small();
+    griddep_wait();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; k++) {
+            const int p = t * top + k;
+            if (pair_expert[p] >= 0) acc += o[(size_t)row_of_pair[p] * D + c];
+        }
+        out[(size_t)t * D + c] = from_f32<bf16>(acc * weight);
+    }
+}
+
 template <typename TA, int BM>
 int launch_products(const void* h, const void* w_gu, const void* w_down, void* y, float* o, const int* perm,
                     const int* tiles, int max_tiles, const MoeArgs& a, cudaStream_t stream) {
@@ -272,6 +353,25 @@ MYNAH_API int mynah_moe_plain(int on) {
     return before;
 }
 
+// From how many (token, choice) pairs a bfloat16 step's products run as grouped tcgen05 products (0: never).
+static int g_moe_grouped_min = 1024;
+MYNAH_API int mynah_moe_grouped_min(int n) {
+    const int before = g_moe_grouped_min;
+    g_moe_grouped_min = n;
+    return before;
+}
+
+extern "C" int mynah_gemm_tcgen05_grouped(const void* A, const void* W, void* C, int M, int N, int K, int ldc, int epilogue, int groups,
+                               int group_rows, const int* tile_group, float gate_limit, float gate_alpha, int sm_count,
+                               int* status, cudaStream_t stream);
+
+// Rows of the sorted, padded layout of a step whose products run grouped; 0: the step runs tile by tile instead.
+MYNAH_API int mynah_moe_grouped_rows(int T, int top, int E, int D, int F, int dtype) {
+    const long long P = (long long)T * top;
+    if (dtype != MYNAH_BF16 || g_moe_plain || g_moe_grouped_min <= 0 || P < g_moe_grouped_min || D % 8 || F % 8) return 0;
+    return (int)((P + (long long)E * (GROUP_TILE - 1) + GROUP_TILE - 1) / GROUP_TILE * GROUP_TILE);
+}
+
 // Rows of a tile for a step of T tokens: small steps (decode) take 16-row tiles, prompts 64-row tiles.
 MYNAH_API int mynah_moe_tile_rows(int T, int top) { return (long long)T * top <= 256 ? 16 : 64; }
 
@@ -279,9 +379,10 @@ MYNAH_API int mynah_moe_tile_rows(int T, int top) { return (long long)T * top <=
 MYNAH_API int mynah_moe_max_tiles(int T, int top, int E) { return ceil_div(T * top, mynah_moe_tile_rows(T, top)) + E; }
 
 // The whole feed-forward. h: [T][D]; table: int32 [V][top]; w_gu: [E][2][F][D]; w_down: [E][D][F]; out: [T][D] in the
-// activation type. Scratch: y [T*top][F] (activation type), o fp32 [T*top][D], ints [2*T*top + 1 + 3*max_tiles].
+// activation type. Scratch, with R = max(T*top, mynah_moe_grouped_rows(...)): y [R][F] (activation type), o fp32 [R][D],
+// ints [2*T*top + 1 + 3*max_tiles + R + R/128], and, when the products run grouped, a [R][D] (activation type; else null).
 MYNAH_API int mynah_moe_table_ffn(const void* h, int dtype, const int* tokens, const int* tok_seq, const int* table,
-                                  const void* w_gu, const void* w_down, void* out, void* y, float* o, int* ints,
+                                  const void* w_gu, const void* w_down, void* out, void* y, float* o, int* ints, void* a_sorted,
                                   int T, int V, int top, int E, int D, int F, float limit, float alpha, float weight,
                                   int* status, cudaStream_t stream) {
     if (T == 0) return 0;
@@ -292,6 +393,22 @@ MYNAH_API int mynah_moe_table_ffn(const void* h, int dtype, const int* tokens, c
     int* pair_expert = ints;
     int* perm = ints + P;
     int* tiles = ints + 2 * P;
+    const int m_pad = mynah_moe_grouped_rows(T, top, E, D, F, dtype);
+    if (m_pad > 0 && a_sorted != nullptr &&
+        (((uintptr_t)h | (uintptr_t)w_gu | (uintptr_t)w_down | (uintptr_t)y | (uintptr_t)a_sorted | (uintptr_t)o) & 15) == 0) {
+        int* perm_pad = ints + 2 * P + 1 + 3 * max_tiles;
+        int* tile_group = perm_pad + m_pad;
+        mynah_launch(moe_route_padded_kernel, dim3(1), dim3(MOE_ROUTE_THREADS), 0, stream, tokens, tok_seq, table, T, V, top, E, m_pad,
+                     pair_expert, perm, perm_pad, tile_group, status);
+        if (mynah_check_launch("moe_route") != 0) return -1;
+        mynah_launch(moe_gather_kernel, dim3(m_pad), dim3(128), 0, stream, (const bf16*)h, (const int*)perm_pad, (bf16*)a_sorted, top, D);
+        if (mynah_check_launch("moe_gather") != 0) return -1;
+        if (mynah_gemm_tcgen05_grouped(a_sorted, w_gu, y, m_pad, F, D, F, 4, E, 2 * F, tile_group, limit, alpha, 0, status, stream) != 0) return -1;
+        if (mynah_gemm_tcgen05_grouped(y, w_down, o, m_pad, D, F, D, 1, E, D, tile_group, 0.f, 0.f, 0, status, stream) != 0) return -1;
+        mynah_launch(moe_combine_rows_kernel, dim3(T), dim3(D >= 1024 ? 256 : 128), 0, stream, (const float*)o, (const int*)pair_expert,
+                     (const int*)perm, (bf16*)out, top, D, weight);
+        return mynah_check_launch("moe_combine");
+    }
     mynah_launch(moe_route_kernel, dim3(1), dim3(MOE_ROUTE_THREADS), 0, stream, tokens, tok_seq, table, T, V, top, E, BM,
                  pair_expert, perm, tiles, max_tiles, status);
     if (mynah_check_launch("moe_route") != 0) return -1;

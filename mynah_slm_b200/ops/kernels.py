@@ -916,6 +916,12 @@ def head_linear_plain(on: bool) -> bool:
     return bool(lib.load().mynah_head_linear_plain(1 if on else 0))
 
 
+def moe_grouped_min(n: int) -> int:
+    """From how many (token, choice) pairs a bfloat16 step's expert products run as grouped tcgen05 products; 0: never
+    (they then run tile by tile on `mma.sync`). Returns the setting before; the two agree to rounding."""
+    return int(lib.load().mynah_moe_grouped_min(int(n)))
+
+
 def moe_plain(on: bool) -> bool:
     """Run the experts' bfloat16 products on the plain tiled kernels instead of the tensor-core ones (the tests compare
     the two). Returns the setting before."""
@@ -936,12 +942,17 @@ def moe_table_ffn(h: torch.Tensor, table: torch.Tensor, w_gu: torch.Tensor, w_do
         raise KernelError("moe_table_ffn: sizes do not fit")
     P_ = T * top
     dev = h.device
+    # rows of the sorted, padded layout when the step's products run as grouped tensor-core products (prompts), else 0
+    grouped = int(lib.load().mynah_moe_grouped_rows(T, top, E, D, F, code(h.dtype)))
+    R = max(P_, grouped)
     out = torch.empty((T, D), dtype=h.dtype, device=dev)
-    y = torch.empty((P_, F), dtype=h.dtype, device=dev)
-    o = torch.empty((P_, D), dtype=torch.float32, device=dev)
-    ints = torch.empty((2 * P_ + 1 + 3 * int(lib.load().mynah_moe_max_tiles(T, top, E)),), dtype=torch.int32, device=dev)
+    y = torch.empty((R, F), dtype=h.dtype, device=dev)
+    o = torch.empty((R, D), dtype=torch.float32, device=dev)
+    a = torch.empty((R, D), dtype=h.dtype, device=dev) if grouped else None
+    ints = torch.empty((2 * P_ + 1 + 3 * int(lib.load().mynah_moe_max_tiles(T, top, E)) + R + R // 128 + 1,),
+                       dtype=torch.int32, device=dev)
     call("mynah_moe_table_ffn", ptr(h), code(h.dtype), ptr(ctx.tokens), ptr(ctx.tok_seq), ptr(table), ptr(w_gu),
-         ptr(w_down), ptr(out), ptr(y), ptr(o), ptr(ints), T, table.shape[0], top, E, D, F, float(limit), float(alpha),
+         ptr(w_down), ptr(out), ptr(y), ptr(o), ptr(ints), ptr(a), T, table.shape[0], top, E, D, F, float(limit), float(alpha),
          1.0 / top, ptr(ctx.status), stream_ptr())
-    lib.add_launches(3)                       # route, two products, combine
+    lib.add_launches(4 if grouped else 3)     # route, (gather,) two products, combine
     return out

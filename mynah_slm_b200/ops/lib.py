@@ -116,7 +116,7 @@ _SIGNATURES: dict[str, list] = {
     "mynah_retention_prep": [P, c_int, c_int, c_int, c_int, P, P, c_int, c_int, c_int, P, P, c_int, c_int, c_int,
                              c_float, P, P, P, P],
     "mynah_retention_scan": [P, P, P, c_int, c_int, c_int, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
-    "mynah_moe_table_ffn": [P, c_int, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
+    "mynah_moe_table_ffn": [P, c_int, P, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_float, c_float, c_float, P, P],
 }
 
@@ -159,11 +159,13 @@ def load() -> ctypes.CDLL:
     lib.mynah_gemm_tcgen05_splits_k.argtypes = [c_int, c_int, c_int, c_int]
     lib.mynah_gemv_decode_supported.restype = c_int
     lib.mynah_gemv_decode_supported.argtypes = [c_int, c_int, c_int]
-    for name in ("mynah_moe_plain", "mynah_retention_chunk_min", "mynah_head_linear_plain"):
+    for name in ("mynah_moe_plain", "mynah_retention_chunk_min", "mynah_head_linear_plain", "mynah_moe_grouped_min"):
         getattr(lib, name).restype = c_int
         getattr(lib, name).argtypes = [c_int]
     lib.mynah_retention_scratch_floats.restype = c_longlong
     lib.mynah_retention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mynah_moe_grouped_rows.restype = c_int
+    lib.mynah_moe_grouped_rows.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int]
     lib.mynah_moe_max_tiles.restype = c_int
     lib.mynah_moe_max_tiles.argtypes = [c_int, c_int, c_int]
     for name, args in _SIGNATURES.items():

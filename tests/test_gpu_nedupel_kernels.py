@@ -195,7 +195,8 @@ def test_retention_prep_and_scan(H, dim, vd, rot):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,D,F,E,top", [(150, 48, 56, 9, 2), (5, 40, 12, 1, 1), (3, 64, 20, 7, 7), (400, 96, 200, 70, 4)])
+@pytest.mark.parametrize("T,D,F,E,top", [(150, 48, 56, 9, 2), (5, 40, 12, 1, 1), (3, 64, 20, 7, 7), (400, 96, 200, 70, 4),
+                                        (700, 128, 320, 5, 2)])
 def test_table_routed_experts(dtype, T, D, F, E, top):
     from mynah_slm_b200.ops import kernels
     rng = np.random.default_rng(T + E)
@@ -218,16 +219,22 @@ def test_table_routed_experts(dtype, T, D, F, E, top):
     assert int(ctx.status.item()) == 0
     assert rel(ref, out[:T]) < (2e-5 if dtype == torch.float32 else 3e-2) and np.all(out[T:] == 0)
     if dtype == torch.bfloat16:
-        # the tensor-core products against the plain tiled ones, and a row's bits in a small step against a large one
+        # three routes to one result: grouped tcgen05 products (large steps), mma.sync tile by tile, plain tiles
+        before = kernels.moe_grouped_min(0)
+        try:
+            tiled = kernels.moe_table_ffn(hp, i32(table), w_gu, w_down, ctx, top, limit, 1.702).float().cpu().numpy()
+            few = ctx_for([2], [0], tokens=list(toks[:2]))
+            small = kernels.moe_table_ffn(hp[:2].contiguous(), i32(table), w_gu, w_down, few, top, limit, 1.702).float().cpu().numpy()
+        finally:
+            kernels.moe_grouped_min(before)
+        assert rel(tiled[:T], out[:T]) < 2e-2 and np.all(tiled[T:] == 0)
+        assert np.array_equal(small, tiled[:2])            # a row's bits in a 16-row tile and in a 64-row tile
         before = kernels.moe_plain(True)
         try:
             plain_out = kernels.moe_table_ffn(hp, i32(table), w_gu, w_down, ctx, top, limit, 1.702).float().cpu().numpy()
         finally:
             kernels.moe_plain(before)
-        assert rel(plain_out[:T], out[:T]) < 2e-2
-        few = ctx_for([2], [0], tokens=list(toks[:2]))
-        small = kernels.moe_table_ffn(hp[:2].contiguous(), i32(table), w_gu, w_down, few, top, limit, 1.702).float().cpu().numpy()
-        assert np.array_equal(small, out[:2])
+        assert rel(plain_out[:T], tiled[:T]) < 2e-2
     # an expert id outside the table's range is reported and skipped
     bad = table.copy()
     bad[toks[0], 0] = E
