@@ -86,7 +86,14 @@ LARGE = config(96, 180, [
     bare(retention(1, 300, 12, [0.9])),
 ])
 
-CONFIGS = {"hybrid": HYBRID, "odd": ODD, "latent": ONLY_LATENT, "retention": ONLY_RETENTION, "moe": ONLY_MOE,
+# a width, a vocabulary and inner sizes that are no multiple of 8 or of 4 anywhere
+RAGGED = config(52, 97, [
+    moe(retention(2, 14, 9, [0.9, 0.8], rot=(10, 33.0)), 18, 1.1, 3, 2),
+    dense(latent(3, 7, 6, 5, 11, 0.4, base=90.0), 30),
+    bare(latent(2, 5, 6, 9, 11, 0.6, base=90.0, kv_from=1)),
+], eps=1e-4, emb=2.0, mult=0.9, logit=1.5)
+
+CONFIGS = {"ragged": RAGGED, "hybrid": HYBRID, "odd": ODD, "latent": ONLY_LATENT, "retention": ONLY_RETENTION, "moe": ONLY_MOE,
            "dense": ONLY_DENSE, "sharp": SHARP, "wide": WIDE, "large": LARGE}
 
 

@@ -86,7 +86,7 @@ def run_pieces(eng, toks, cuts):
 
 # ------------------------------------------------------------------ each mechanism alone, whole prompts
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["latent", "retention", "moe", "dense", "hybrid", "odd"])
+@pytest.mark.parametrize("name", ["latent", "retention", "moe", "dense", "hybrid", "odd", "ragged"])
 def test_whole_prompts(models, name, dtype):
     _, cfg, W = models[name]
     eng = engine(models, name, dtype)
@@ -112,7 +112,7 @@ def test_layers_one_by_one(models):
 
 # ------------------------------------------------------------------ prefill against decoding, pieces
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["hybrid", "odd"])
+@pytest.mark.parametrize("name", ["hybrid", "odd", "ragged"])
 def test_token_by_token(models, name, dtype):
     _, cfg, W = models[name]
     eng = engine(models, name, dtype)

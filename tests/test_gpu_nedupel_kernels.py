@@ -137,7 +137,7 @@ def plain_retention_core(q, k, v, decay, S0=None):
 
 
 @pytest.mark.parametrize("H,dim,vd,rot", [(3, 16, 24, 16), (1, 33, 5, 6), (2, 128, 64, 0), (2, 300, 12, 64), (2, 256, 40, 64),
-                                          (4, 32, 70, 32), (2, 64, 32, 64)])
+                                          (4, 32, 70, 32), (2, 64, 32, 64), (1, 96, 24, 32), (2, 160, 16, 0), (1, 192, 8, 64)])
 def test_retention_prep_and_scan(H, dim, vd, rot):
     from mynah_slm_b200.ops import kernels
     from mynah_slm_b200.parts.position import rotary_frequencies
