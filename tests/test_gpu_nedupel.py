@@ -388,6 +388,48 @@ def test_greedy_generation(models, name):
             seq.append(r.tokens[t])
 
 
+def test_command_line(models, tmp_path):
+    """`mynah-slm run` on a folder (greedy tokens against the plain implementation, the prompts' logits written beside),
+    sampling with a temperature, and `mynah-slm random` + `run --random` making the same model twice."""
+    import subprocess
+    import sys
+    folder, cfg, W = models["hybrid"]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cli = [sys.executable, os.path.join(root, "bin", "mynah-slm")]
+    a, b = tokens_for(cfg, 40, 401), tokens_for(cfg, 3, 402)
+    ids = lambda t: ",".join(str(x) for x in t)
+    npy = tmp_path / "logits.npy"
+    p = subprocess.run(cli + ["run", "-m", folder, "--tokens", ids(a), "--tokens", ids(b), "-n", "5", "--temp", "0", "--dtype", "float32",
+                              "--ignore-eos", "--quiet", "--logits-out", str(npy)], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [[int(x) for x in l.split()] for l in p.stdout.strip().splitlines()]
+    assert len(lines) == 2 and all(len(l) == 5 for l in lines)
+    ra, rb = plain.forward(cfg, W, a), plain.forward(cfg, W, b)
+    assert_close(np.concatenate([ra, rb]), np.load(npy), FP32_TOL, "--logits-out")
+    for prompt, got in ((a, lines[0]), (b, lines[1])):
+        seq = list(prompt)
+        for t in range(5):
+            logits = plain.forward(cfg, W, seq)[-1]
+            top2 = np.sort(logits)[-2:]
+            if top2[1] - top2[0] < 1e-3 * max(1.0, abs(top2[1])):
+                break
+            assert got[t] == int(np.argmax(logits))
+            seq.append(got[t])
+    s = subprocess.run(cli + ["run", "-m", folder, "--tokens", ids(a), "-n", "12", "--temp", "0.8", "--top-k", "20", "--seed", "3",
+                              "--ignore-eos", "--quiet"], capture_output=True, text=True, timeout=600)
+    assert s.returncode == 0 and len(s.stdout.split()) == 12 and all(0 <= int(x) < cfg["vocab"] for x in s.stdout.split())
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(cfg))
+    w = subprocess.run(cli + ["random", "-o", str(tmp_path / "made"), "--config", str(cfg_path), "--seed", "4", "--dtype", "bfloat16"],
+                       capture_output=True, text=True, timeout=600)
+    assert w.returncode == 0, w.stderr[-2000:]
+    runs = [subprocess.run(cli + src + ["--tokens", ids(b), "-n", "6", "--temp", "0", "--ignore-eos", "--quiet"],
+                           capture_output=True, text=True, timeout=600)
+            for src in (["run", "-m", str(tmp_path / "made")], ["run", "--random", str(cfg_path), "--weights-seed", "4"])]
+    assert all(r.returncode == 0 for r in runs), runs[0].stderr[-1000:] + runs[1].stderr[-1000:]
+    assert runs[0].stdout.split() == runs[1].stdout.split() and len(runs[0].stdout.split()) == 6
+
+
 def test_trace_runner_process(models, tmp_path):
     """bin/trace_run as a process: a batch of two prompts, decoding together, one ends early."""
     import subprocess
